@@ -16,6 +16,20 @@
 //
 //   combine   the last step of `attend` alone, for maps that another kernel has attended (float [T, H*M, Dv]).
 //
+// Mixing of the softmax weights across heads (Shazeer et al., "Talking-Heads Attention", mix the weights of all heads
+// after the softmax):  w'_h(t, s) = sum_g T[h, g] w_g(t, s), and head h applies w'_h to the values of its own
+// key/value head c(h).  Since the mixing is linear and every w_g is normalised by itself,
+//     o_h = sum_g T[h, g] A[g, c(h)],    A[g, c] = sum_s w_g(t, s) v_c(s),
+// so the attention of head g over the values of ALL key/value heads is computed once (the values of a token's heads
+// lie side by side in one row of G*Dv numbers: value pages [n_pages, 1, page, G*Dv]) and the mixing is a small
+// product afterwards.  The query vectors are then ordered so that vector x reads key head x % G (the order of the
+// general tensor-core kernel with G maps in one group): head g = (x % G) * (H/G) + x / G.
+//   talk_attend   one warp per (token, query vector x): A[t, x, :] in float32, running softmax in key order
+//   talk_combine  one warp per (token, head h): o_h from A and T, times sigmoid of a gate (optional)
+//
+// `prepare` can divide every value vector by its root mean square (no weight) before it is stored, and can store
+// the value heads side by side.
+//
 // Key pages [n_pages, G*M, page, Dk], value pages [n_pages, G, page, Dv]; one block table for both.
 // Rotation: the first n_rot dims of a vector, pairing 0 = (2i, 2i+1), 1 = (i, i + n_rot/2); tables
 // float32 [positions, n_rot/2].  (u, v) -> (u cos - v sin, v cos + u sin).
@@ -38,6 +52,8 @@ struct PrepareArgs {
   void* k_pages; void* v_pages; int page_size;
   int n_tokens, write_cache;
   const float* bias;       // [stride] or null: added to the projected values first (a projection that left it out)
+  int v_norm;              // 1: a value vector is divided by its root mean square (eps inside the root) before it is stored
+  int v_side_by_side;      // 1: value pages [n_pages, 1, page, n_v * Dv]: a token's value heads in one row
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -67,7 +83,20 @@ attention_prepare_kernel(PrepareArgs a) {
     const int g = vec - a.n_q - a.n_k;
     const int col = a.off_v + g * a.Dv;
     const T* src = row + col;
-    T* dst = reinterpret_cast<T*>(a.v_pages) + (((size_t)page * a.n_v + g) * a.page_size + in_page) * a.Dv;
+    T* dst = a.v_side_by_side
+                 ? reinterpret_cast<T*>(a.v_pages) + (((size_t)page * a.page_size + in_page) * a.n_v + g) * a.Dv
+                 : reinterpret_cast<T*>(a.v_pages) + (((size_t)page * a.n_v + g) * a.page_size + in_page) * a.Dv;
+    if (a.v_norm) {
+      float ss = 0.f;
+      for (int d = lane; d < a.Dv; d += 32) {
+        const float v = to_f32(src[d]) + (a.bias != nullptr ? a.bias[col + d] : 0.f);
+        ss += v * v;
+      }
+      const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)a.Dv + a.eps);
+      for (int d = lane; d < a.Dv; d += 32)
+        dst[d] = from_f32<T>((to_f32(src[d]) + (a.bias != nullptr ? a.bias[col + d] : 0.f)) * inv);
+      return;
+    }
     if (a.bias == nullptr) {
       for (int d = lane; d < a.Dv; d += 32) dst[d] = src[d];
     } else {
@@ -147,8 +176,11 @@ attention_prepare_vec_kernel(PrepareArgs a, int P, int vec_per_warp, long long q
       raw.w = pack2(__uint_as_float(raw.w << 16) + b1.z, __uint_as_float(raw.w & 0xffff0000u) + b1.w);
     }
     const int page = a.block_table[(size_t)b * a.table_width + pos / a.page_size];
-    bf16* dst = reinterpret_cast<bf16*>(a.v_pages) +
-                (((size_t)page * a.n_v + g) * a.page_size + pos % a.page_size) * a.Dv + piece * 8;
+    bf16* dst = a.v_side_by_side
+                    ? reinterpret_cast<bf16*>(a.v_pages) +
+                          (((size_t)page * a.page_size + pos % a.page_size) * a.n_v + g) * a.Dv + piece * 8
+                    : reinterpret_cast<bf16*>(a.v_pages) +
+                          (((size_t)page * a.n_v + g) * a.page_size + pos % a.page_size) * a.Dv + piece * 8;
     *reinterpret_cast<uint4*>(dst) = raw;
     return;
   }
@@ -407,22 +439,42 @@ AB_API int ab_maps_combine(const float* a, void* out, int dtype, const int* tok_
   return ab_launch_status();
 }
 
+AB_API int ab_attention_prepare_opts(void* buf, int dtype, int stride, int off_q, int off_k, int off_v, int n_q, int n_k,
+                                     int n_v, int Dk, int Dv, const float* q_weight, const float* k_weight, float eps,
+                                     const float* cos_t, const float* sin_t, int n_rot, int pairing, const int* tok_pos,
+                                     const int* tok_seq, const int* block_table, int table_width, void* k_pages,
+                                     void* v_pages, int page_size, int n_tokens, int write_cache, const float* bias,
+                                     int v_norm, int v_side_by_side, cudaStream_t stream);
+
 AB_API int ab_attention_prepare(void* buf, int dtype, int stride, int off_q, int off_k, int off_v, int n_q, int n_k,
                                 int n_v, int Dk, int Dv, const float* q_weight, const float* k_weight, float eps,
                                 const float* cos_t, const float* sin_t, int n_rot, int pairing, const int* tok_pos,
                                 const int* tok_seq, const int* block_table, int table_width, void* k_pages,
                                 void* v_pages, int page_size, int n_tokens, int write_cache, const float* bias,
                                 cudaStream_t stream) {
+  return ab_attention_prepare_opts(buf, dtype, stride, off_q, off_k, off_v, n_q, n_k, n_v, Dk, Dv, q_weight, k_weight, eps,
+                                   cos_t, sin_t, n_rot, pairing, tok_pos, tok_seq, block_table, table_width, k_pages,
+                                   v_pages, page_size, n_tokens, write_cache, bias, 0, 0, stream);
+}
+
+// `v_norm`: value vectors are divided by their root mean square before they are stored; `v_side_by_side`: value pages
+// [n_pages, 1, page, n_v * Dv].
+AB_API int ab_attention_prepare_opts(void* buf, int dtype, int stride, int off_q, int off_k, int off_v, int n_q, int n_k,
+                                     int n_v, int Dk, int Dv, const float* q_weight, const float* k_weight, float eps,
+                                     const float* cos_t, const float* sin_t, int n_rot, int pairing, const int* tok_pos,
+                                     const int* tok_seq, const int* block_table, int table_width, void* k_pages,
+                                     void* v_pages, int page_size, int n_tokens, int write_cache, const float* bias,
+                                     int v_norm, int v_side_by_side, cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
   if (Dk <= 0 || Dk > AM_MAX_DIM || Dv <= 0 || n_q < 0 || n_k < 0 || n_v < 0 || page_size <= 0) return AB_BAD_ARG;
   if (n_rot < 0 || n_rot > Dk || (n_rot & 1) || pairing < 0 || pairing > 1) return AB_BAD_ARG;
   if (!cos_t || !sin_t || n_rot == 0) { cos_t = sin_t = nullptr; n_rot = 0; }
   PrepareArgs a{buf, stride, off_q, off_k, off_v, n_q, n_k, n_v, Dk, Dv, q_weight, k_weight, eps, cos_t, sin_t, n_rot,
                 pairing, tok_pos, tok_seq, block_table, table_width, k_pages, v_pages, page_size, n_tokens, write_cache,
-                bias};
+                bias, v_norm ? 1 : 0, v_side_by_side ? 1 : 0};
   const long long warps = (long long)n_tokens * (n_q + n_k + n_v);
   const unsigned blocks = (unsigned)((warps + 3) / 4);
-  const bool pieces = dtype == AB_BF16 && Dk % 8 == 0 && Dv % 8 == 0 && stride % 8 == 0 && off_q % 8 == 0 &&
+  const bool pieces = !v_norm && dtype == AB_BF16 && Dk % 8 == 0 && Dv % 8 == 0 && stride % 8 == 0 && off_q % 8 == 0 &&
                       off_k % 8 == 0 && off_v % 8 == 0 && (n_rot == 0 || pairing == 0 || n_rot % 16 == 0);
   if (pieces) {
     const int P = Dk / 8, vpw = 32 / P;
@@ -470,4 +522,165 @@ AB_API int ab_attention_maps(const void* q, int q_stride, void* out, int dtype, 
   if (dtype == AB_F32) return launch_attend<float>(a, stream);
   if (dtype == AB_BF16) return launch_attend<bf16>(a, stream);
   return AB_BAD_ARG;
+}
+
+
+// ---------------------------------------------------------------------------
+// softmax weights mixed across heads
+// ---------------------------------------------------------------------------
+struct TalkArgs {
+  const void* q; int q_stride;      // query vector x of token t at q + t*q_stride + x*Dk; it reads key head x % G
+  float* A;                         // [T, H, G*Dv]
+  const void* k_pages;              // [n_pages, G, page, Dk]
+  const void* v_pages;              // [n_pages, 1, page, G*Dv]
+  const int* block_table; int table_width;
+  const int* tok_pos; const int* tok_seq;
+  int n_tokens, H, G, Dk, Dv, page_size;
+  float scale; int window;
+};
+
+template <typename T, int KPL, int VPL>
+__global__ void __launch_bounds__(128)
+talk_attend_kernel(TalkArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)a.n_tokens * a.H) return;
+  const int t = (int)(w / a.H), x = (int)(w - (long long)t * a.H);
+  const int Dk = a.Dk, W = a.G * a.Dv;
+  float* o = a.A + (size_t)w * W;
+  const int b = a.tok_seq[t];
+  if (b < 0) {
+    for (int d = lane; d < W; d += 32) o[d] = 0.f;
+    return;
+  }
+  const int pos = a.tok_pos[t];
+  const int kh = x % a.G;
+  const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+  const int* bt = a.block_table + (size_t)b * a.table_width;
+  const T* kp = reinterpret_cast<const T*>(a.k_pages);
+  const T* vp = reinterpret_cast<const T*>(a.v_pages);
+  const T* qv = reinterpret_cast<const T*>(a.q) + (size_t)t * a.q_stride + (size_t)x * Dk;
+  float qr[KPL], acc[VPL];
+#pragma unroll
+  for (int j = 0; j < KPL; ++j) {
+    const int d = lane + 32 * j;
+    qr[j] = d < Dk ? to_f32(qv[d]) : 0.f;
+  }
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) acc[j] = 0.f;
+  float mx = -INFINITY, l = 0.f;
+  for (int s = lo; s <= pos; ++s) {
+    const int page = bt[s / a.page_size], in_page = s % a.page_size;
+    const T* kv = kp + (((size_t)page * a.G + kh) * a.page_size + in_page) * Dk;
+    const T* vv = vp + ((size_t)page * a.page_size + in_page) * W;
+    float part = 0.f;
+#pragma unroll
+    for (int j = 0; j < KPL; ++j) {
+      const int d = lane + 32 * j;
+      if (d < Dk) part += qr[j] * to_f32(kv[d]);
+    }
+    const float score = warp_sum(part) * a.scale;
+    const float m_new = fmaxf(mx, score);
+    const float corr = expf(mx - m_new);   // exp(-inf) = 0 on the first key
+    const float p = expf(score - m_new);
+    l = l * corr + p;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int d = lane + 32 * j;
+      if (d < W) acc[j] = acc[j] * corr + p * to_f32(vv[d]);
+    }
+    mx = m_new;
+  }
+  const float inv = 1.0f / l;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int d = lane + 32 * j;
+    if (d < W) o[d] = acc[j] * inv;
+  }
+}
+
+// out[t, h, d] = gate * sum_g T[h, g] A[t, x(g), c(h)*Dv + d], x(g) = (g % R) * G + g / R, c(h) = h / R, R = H / G;
+// gate = sigmoid(gate_rows[t*gate_stride + h*Dv + d]) or 1.  One warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128)
+talk_combine_kernel(const float* __restrict__ A, const float* __restrict__ talk, const T* __restrict__ gate_rows,
+                    int gate_stride, T* __restrict__ out, const int* __restrict__ tok_seq, int n_tokens, int H, int G,
+                    int Dv) {
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)n_tokens * H) return;
+  const int t = (int)(w / H), h = (int)(w - (long long)t * H);
+  T* o = out + (size_t)w * Dv;
+  if (tok_seq[t] < 0) {
+    for (int d = lane; d < Dv; d += 32) o[d] = from_f32<T>(0.f);
+    return;
+  }
+  const int R = H / G, c = h / R, W = G * Dv;
+  const float* At = A + (size_t)t * H * W + (size_t)c * Dv;
+  const float* Th = talk + (size_t)h * H;
+  for (int d = lane; d < Dv; d += 32) {
+    float sum = 0.f;
+    for (int g = 0; g < H; ++g) sum = fmaf(Th[g], At[(size_t)((g % R) * G + g / R) * W + d], sum);
+    if (gate_rows != nullptr) sum *= 1.0f / (1.0f + expf(-to_f32(gate_rows[(size_t)t * gate_stride + h * Dv + d])));
+    o[d] = from_f32<T>(sum);
+  }
+}
+
+template <typename T>
+static int launch_talk(const TalkArgs& a, cudaStream_t stream) {
+  const long long warps = (long long)a.n_tokens * a.H;
+  const unsigned blocks = (unsigned)((warps + 3) / 4);
+  const int W = a.G * a.Dv;
+  const int kc = a.Dk <= 64 ? 2 : (a.Dk <= 128 ? 4 : 8);
+#define AB_GO(KPL, VPL) ab_launch(talk_attend_kernel<T, KPL, VPL>, dim3(blocks), dim3(128), 0, stream, a)
+#define AB_V(KPL)                                   \
+  if (W <= 64) AB_GO(KPL, 2);                       \
+  else if (W <= 128) AB_GO(KPL, 4);                 \
+  else if (W <= 256) AB_GO(KPL, 8);                 \
+  else if (W <= 512) AB_GO(KPL, 16);                \
+  else if (W <= 1024) AB_GO(KPL, 32);               \
+  else AB_GO(KPL, 64);
+  if (kc == 2) { AB_V(2) } else if (kc == 4) { AB_V(4) } else { AB_V(8) }
+#undef AB_V
+#undef AB_GO
+  return ab_launch_status();
+}
+
+#define TALK_MAX_ROW 2048      // G * Dv: the numbers of a token's values that a warp holds sums for
+
+AB_API int ab_talk_max_row() { return TALK_MAX_ROW; }
+
+AB_API int ab_talk_attend(const void* q, int q_stride, float* A, int dtype, const void* k_pages, const void* v_pages,
+                          const int* block_table, int table_width, const int* tok_pos, const int* tok_seq, int n_tokens,
+                          int H, int G, int Dk, int Dv, int page_size, float scale, int window, cudaStream_t stream) {
+  if (n_tokens <= 0) return AB_OK;
+  if (Dk <= 0 || Dk > AM_MAX_DIM || Dv <= 0 || H <= 0 || G <= 0 || H % G || (long long)G * Dv > TALK_MAX_ROW ||
+      page_size <= 0)
+    return AB_BAD_ARG;
+  TalkArgs a{q, q_stride, A, k_pages, v_pages, block_table, table_width, tok_pos, tok_seq, n_tokens, H, G, Dk, Dv,
+             page_size, scale, window};
+  if (dtype == AB_F32) return launch_talk<float>(a, stream);
+  if (dtype == AB_BF16) return launch_talk<bf16>(a, stream);
+  return AB_BAD_ARG;
+}
+
+AB_API int ab_talk_combine(const float* A, const float* talk, const void* gate_rows, int gate_stride, void* out, int dtype,
+                           const int* tok_seq, int n_tokens, int H, int G, int Dv, cudaStream_t stream) {
+  if (n_tokens <= 0) return AB_OK;
+  if (H <= 0 || G <= 0 || H % G || Dv <= 0) return AB_BAD_ARG;
+  const long long warps = (long long)n_tokens * H;
+  const unsigned blocks = (unsigned)((warps + 3) / 4);
+  if (dtype == AB_F32)
+    ab_launch(talk_combine_kernel<float>, dim3(blocks), dim3(128), 0, stream, A, talk, (const float*)gate_rows, gate_stride,
+              (float*)out, tok_seq, n_tokens, H, G, Dv);
+  else if (dtype == AB_BF16)
+    ab_launch(talk_combine_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, A, talk, (const bf16*)gate_rows, gate_stride,
+              (bf16*)out, tok_seq, n_tokens, H, G, Dv);
+  else
+    return AB_BAD_ARG;
+  return ab_launch_status();
 }

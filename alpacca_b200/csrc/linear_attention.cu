@@ -23,6 +23,12 @@
 // The state of a sequence is read when the step starts and written back when it ends, so a prompt may be cut
 // anywhere and a decode step is the same code with one token.  The projections come as one float32 row per
 // token: zq | zk | zv | g at given offsets.
+//
+// Options (retention: Sun et al., "Retentive Network: A Successor to Transformer for Large Language Models", has
+// this recurrence with rotated q and k): no activation on q, k, v; a rotation by position of the first n_rot dims
+// of every q and k vector (pairs (2i, 2i+1) or (i, i + n_rot/2), tables float32 [positions, n_rot/2]); k times a
+// constant after the rotation; the root mean square taken per head instead of over all heads, with or without a
+// weight; silu instead of sigmoid on the gate.
 #include "common.cuh"
 #include "launch.cuh"
 
@@ -43,9 +49,34 @@ struct LinAttnArgs {
   const int* item_t0;      // [n_items] its first packed token
   const int* item_t1;      // [n_items] one past its last
   float* pieces;           // [n_items, H, D, V]
+  // what happens to the projections before the recurrence
+  int act;                 // 1: silu on q, k, v; 0: none
+  const float* cos_t;      // [positions, n_rot / 2] or null: no rotation
+  const float* sin_t;
+  int n_rot, pairing;      // pairing 0: (2i, 2i+1), 1: (i, i + n_rot/2)
+  const int* tok_pos;      // [T]
+  float k_scale;           // k is multiplied by this after the rotation
 };
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+// element d of a q or k vector `vec` (D floats as projected) after activation and rotation by position `pos`
+__device__ __forceinline__ float la_prepared(const LinAttnArgs& a, const float* __restrict__ vec, int d, int pos) {
+  float v = vec[d];
+  if (a.act) v = silu_f(v);
+  if (a.cos_t != nullptr && d < a.n_rot) {
+    const int half = a.n_rot >> 1;
+    int i, partner;
+    bool first;
+    if (a.pairing == 0) { i = d >> 1; first = (d & 1) == 0; partner = d ^ 1; }
+    else { first = d < half; i = first ? d : d - half; partner = first ? d + half : d - half; }
+    float p = vec[partner];
+    if (a.act) p = silu_f(p);
+    const float c = a.cos_t[(size_t)pos * half + i], sn = a.sin_t[(size_t)pos * half + i];
+    v = first ? v * c - p * sn : v * c + p * sn;
+  }
+  return v;
+}
 
 #define LA_COLS 32
 #define LA_SLICES 4
@@ -81,12 +112,18 @@ linattn_walk_kernel(LinAttnArgs a) {
     for (int i = tid; i < n * DP; i += LA_COLS * LA_SLICES) {
       const int tok = i / DP, d = i - tok * DP;
       const float* row = a.proj + (size_t)(tb + tok) * a.ld;
-      qs[tok][d] = d < D ? silu_f(row[a.off_q + h * D + d]) : 0.f;
-      ks[tok][d] = d < D ? silu_f(row[a.off_k + h * D + d]) : 0.f;
+      const int pos = a.cos_t != nullptr ? a.tok_pos[tb + tok] : 0;
+      qs[tok][d] = d < D ? la_prepared(a, row + a.off_q + h * D, d, pos) : 0.f;
+      ks[tok][d] = d < D ? la_prepared(a, row + a.off_k + h * D, d, pos) * a.k_scale : 0.f;
     }
     for (int i = tid; i < n * LA_COLS; i += LA_COLS * LA_SLICES) {
       const int tok = i / LA_COLS, cc = i - tok * LA_COLS;
-      vs[tok][cc] = (c0 + cc < V) ? silu_f(a.proj[(size_t)(tb + tok) * a.ld + a.off_v + h * V + c0 + cc]) : 0.f;
+      float v = 0.f;
+      if (c0 + cc < V) {
+        v = a.proj[(size_t)(tb + tok) * a.ld + a.off_v + h * V + c0 + cc];
+        if (a.act) v = silu_f(v);
+      }
+      vs[tok][cc] = v;
     }
     __syncthreads();
     for (int tok = 0; tok < n; ++tok) {
@@ -137,6 +174,28 @@ __global__ void linattn_activate_kernel(float* __restrict__ proj, int ld, int c0
   if (tok_seq[t] < 0) return;
   float* p = proj + t * ld + c0 + (i - t * w);
   *p = silu_f(*p);
+}
+
+// q and k of every token in place: activation, rotation, k's constant.  One warp per (token, q or k vector).
+__global__ void __launch_bounds__(128)
+linattn_prepare_kernel(LinAttnArgs a, int n_tokens) {
+  __shared__ float stage[4][256];
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const long long w = (long long)blockIdx.x * 4 + wib;
+  if (w >= (long long)n_tokens * 2 * a.H) return;
+  const int t = (int)(w / (2 * a.H)), vec = (int)(w - (long long)t * 2 * a.H);
+  if (a.tok_seq[t] < 0) return;
+  const bool is_k = vec >= a.H;
+  const int h = is_k ? vec - a.H : vec;
+  float* row = const_cast<float*>(a.proj) + (size_t)t * a.ld + (is_k ? a.off_k : a.off_q) + h * a.D;
+  const int pos = a.cos_t != nullptr ? a.tok_pos[t] : 0;
+  const float mul = is_k ? a.k_scale : 1.0f;
+  float* x = stage[wib];
+  for (int d = lane; d < a.D; d += 32) x[d] = la_prepared(a, row, d, pos) * mul;
+  __syncwarp();
+  for (int d = lane; d < a.D; d += 32) row[d] = x[d];
 }
 
 __device__ __forceinline__ void la_cp_async_16(void* smem, const void* gmem) {
@@ -367,7 +426,7 @@ AB_API int ab_linear_attention_stream_cols(int D) { return D % 64 == 0 ? 8 : 32;
 template <typename T>
 __global__ void linattn_output_kernel(const float* __restrict__ o_raw, const float* __restrict__ proj, int ld, int off_g,
                                       const float* __restrict__ weight, const int* __restrict__ tok_seq,
-                                      T* __restrict__ out, int n, float eps) {
+                                      T* __restrict__ out, int n, float eps, int gate_silu) {
   __shared__ float scratch[32];
   pdl_wait();
   pdl_trigger();
@@ -384,8 +443,38 @@ __global__ void linattn_output_kernel(const float* __restrict__ o_raw, const flo
   const float inv = 1.0f / sqrtf(ss / (float)n + eps);
   const float* g = proj + (size_t)t * ld + off_g;
   for (int j = threadIdx.x; j < n; j += blockDim.x) {
-    const float gate = 1.0f / (1.0f + expf(-g[j]));
+    const float gate = (gate_silu ? g[j] : 1.0f) / (1.0f + expf(-g[j]));
     y[j] = from_f32<T>(o[j] * inv * weight[j] * gate);
+  }
+}
+
+// The root mean square per head: out[t, h, j] = o[t, h, j] / rms(o[t, h, :]) * weight[h, j] (weight null: 1) * gate.
+// One warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128)
+linattn_output_head_kernel(const float* __restrict__ o_raw, const float* __restrict__ proj, int ld, int off_g,
+                           const float* __restrict__ weight, const int* __restrict__ tok_seq, T* __restrict__ out,
+                           int n_tokens, int H, int V, float eps, int gate_silu) {
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (w >= (long long)n_tokens * H) return;
+  const int t = (int)(w / H), h = (int)(w - (long long)t * H);
+  T* y = out + (size_t)w * V;
+  if (tok_seq[t] < 0) {
+    for (int j = lane; j < V; j += 32) y[j] = from_f32<T>(0.f);
+    return;
+  }
+  const float* o = o_raw + (size_t)w * V;
+  float ss = 0.f;
+  for (int j = lane; j < V; j += 32) ss += o[j] * o[j];
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+  const float* g = proj + (size_t)t * ld + off_g + h * V;
+  for (int j = lane; j < V; j += 32) {
+    const float gate = (gate_silu ? g[j] : 1.0f) / (1.0f + expf(-g[j]));
+    y[j] = from_f32<T>(o[j] * inv * (weight != nullptr ? weight[h * V + j] : 1.0f) * gate);
   }
 }
 
@@ -395,7 +484,7 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(256)
 linattn_output_vec_kernel(const float* __restrict__ o_raw, const float* __restrict__ proj, int ld, int off_g,
                           const float* __restrict__ weight, const int* __restrict__ tok_seq, T* __restrict__ out, int n,
-                          float eps) {
+                          float eps, int gate_silu) {
   __shared__ float scratch[32];
   pdl_wait();
   pdl_trigger();
@@ -426,10 +515,10 @@ linattn_output_vec_kernel(const float* __restrict__ o_raw, const float* __restri
     const int i = threadIdx.x + k * 256;
     if (i < n4) {
       const float4 wv = wr[i];
-      y[4 * i] = from_f32<T>(ov[k].x * inv * wv.x / (1.0f + expf(-gv[k].x)));
-      y[4 * i + 1] = from_f32<T>(ov[k].y * inv * wv.y / (1.0f + expf(-gv[k].y)));
-      y[4 * i + 2] = from_f32<T>(ov[k].z * inv * wv.z / (1.0f + expf(-gv[k].z)));
-      y[4 * i + 3] = from_f32<T>(ov[k].w * inv * wv.w / (1.0f + expf(-gv[k].w)));
+      y[4 * i] = from_f32<T>(ov[k].x * inv * wv.x * (gate_silu ? gv[k].x : 1.0f) / (1.0f + expf(-gv[k].x)));
+      y[4 * i + 1] = from_f32<T>(ov[k].y * inv * wv.y * (gate_silu ? gv[k].y : 1.0f) / (1.0f + expf(-gv[k].y)));
+      y[4 * i + 2] = from_f32<T>(ov[k].z * inv * wv.z * (gate_silu ? gv[k].z : 1.0f) / (1.0f + expf(-gv[k].z)));
+      y[4 * i + 3] = from_f32<T>(ov[k].w * inv * wv.w * (gate_silu ? gv[k].w : 1.0f) / (1.0f + expf(-gv[k].w)));
     }
   }
 }
@@ -457,34 +546,54 @@ AB_API int ab_linear_attention_max_dim() { return 64 * LA_SLICES; }
 // sequences side by side: piece p is the packed tokens item_t0[p] .. item_t1[p] - 1 of sequence item_seq[p]; the pieces
 // of sequence b are seq_first[b] .. seq_first[b] + seq_count[b] - 1, in order, and cover its tokens; `pieces` is
 // scratch, float [n_items, H, D, V].
-AB_API int ab_linear_attention_step(const float* proj, int ld, int off_q, int off_k, int off_v, int off_g,
-                                    const float* decay, float* state, int H, int D, int V, const int* cu_q,
-                                    const int* slots, const int* tok_seq, int n_seqs, int n_tokens, float* o_raw,
-                                    const float* weight, float eps, void* out, int out_dtype, int write_state,
-                                    int stream_from, const int* item_seq, const int* item_t0, const int* item_t1,
-                                    int n_items, float* pieces, const int* seq_first, const int* seq_count,
-                                    cudaStream_t stream) {
+//
+// The options: `act` 1 = silu on q, k, v, 0 = none; cos_t, sin_t (or null), n_rot, pairing, tok_pos: the rotation of q
+// and k; k_scale; `head_norm` 1 = the root mean square per head, 0 = over all heads; `weight` may be null with
+// head_norm (no weight); `gate_silu` 1 = silu(g), 0 = sigmoid(g).
+AB_API int ab_linear_attention_step_opts(const float* proj, int ld, int off_q, int off_k, int off_v, int off_g,
+                                         const float* decay, float* state, int H, int D, int V, const int* cu_q,
+                                         const int* slots, const int* tok_seq, int n_seqs, int n_tokens, float* o_raw,
+                                         const float* weight, float eps, void* out, int out_dtype, int write_state,
+                                         int stream_from, const int* item_seq, const int* item_t0, const int* item_t1,
+                                         int n_items, float* pieces, const int* seq_first, const int* seq_count,
+                                         int act, const float* cos_t, const float* sin_t, int n_rot, int pairing,
+                                         const int* tok_pos, float k_scale, int head_norm, int gate_silu,
+                                         cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return AB_OK;
   if (H <= 0 || D <= 0 || V <= 0 || D > 64 * LA_SLICES || H > 65535) return AB_BAD_ARG;
+  if (n_rot < 0 || n_rot > D || (n_rot & 1) || pairing < 0 || pairing > 1) return AB_BAD_ARG;
+  if (!cos_t || !sin_t || n_rot == 0) { cos_t = sin_t = nullptr; n_rot = 0; }
+  if (cos_t && !tok_pos) return AB_BAD_ARG;
+  if (!weight && !head_norm) return AB_BAD_ARG;
   LinAttnArgs a{proj, ld, off_q, off_k, off_v, off_g, decay, state, H, D, V, cu_q, slots, tok_seq, o_raw, write_state,
-                0, nullptr, nullptr, nullptr, nullptr};
+                0, nullptr, nullptr, nullptr, nullptr, act ? 1 : 0, cos_t, sin_t, n_rot, pairing, tok_pos, k_scale};
+  const bool plain_qk = cos_t == nullptr && k_scale == 1.0f;     // q and k need the activation at most
   const unsigned col_tiles = (unsigned)((V + LA_COLS - 1) / LA_COLS);
   if (col_tiles > 65535) return AB_BAD_ARG;
   int rc;
   const bool aligned = D % 4 == 0 && ld % 4 == 0 && off_q % 4 == 0 && off_k % 4 == 0;
   if (aligned && n_tokens > stream_from * n_seqs) {
-    // prompts: activation in place, then the walk on rows that cp.async brings
-    const int c0 = off_q < off_k ? off_q : off_k, c1 = off_v + H * V;
+    // prompts: activation (and rotation, and k's constant) in place, then the walk on rows that cp.async brings
     if (!(off_k == off_q + H * D && off_v == off_k + H * D)) return AB_BAD_ARG;   // q | k | v side by side
-    const size_t total = (size_t)n_tokens * (c1 - c0);
-    if (c0 % 4 == 0 && (c1 - c0) % 4 == 0)
-      ab_launch(linattn_activate4_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, stream,
-                const_cast<float*>(proj), ld, c0, c1, tok_seq, n_tokens);
-    else
-      ab_launch(linattn_activate_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
-                const_cast<float*>(proj), ld, c0, c1, tok_seq, n_tokens);
-    rc = ab_launch_status();
-    if (rc) return rc;
+    if (!plain_qk) {
+      const long long warps = (long long)n_tokens * 2 * H;
+      ab_launch(linattn_prepare_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, a, n_tokens);
+      rc = ab_launch_status();
+      if (rc) return rc;
+    }
+    // what is left for the activation: q | k | v, or v alone when q and k were prepared above
+    const int c0 = plain_qk ? (off_q < off_k ? off_q : off_k) : off_v, c1 = off_v + H * V;
+    if (act) {
+      const size_t total = (size_t)n_tokens * (c1 - c0);
+      if (c0 % 4 == 0 && (c1 - c0) % 4 == 0)
+        ab_launch(linattn_activate4_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, stream,
+                  const_cast<float*>(proj), ld, c0, c1, tok_seq, n_tokens);
+      else
+        ab_launch(linattn_activate_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                  const_cast<float*>(proj), ld, c0, c1, tok_seq, n_tokens);
+      rc = ab_launch_status();
+      if (rc) return rc;
+    }
     if (n_items > 0) {
       if (!item_seq || !item_t0 || !item_t1 || !pieces || !seq_first || !seq_count) return AB_BAD_ARG;
       a.item_seq = item_seq; a.item_t0 = item_t0; a.item_t1 = item_t1; a.pieces = pieces;
@@ -517,9 +626,22 @@ AB_API int ab_linear_attention_step(const float* proj, int ld, int off_q, int of
   }
   if (rc) return rc;
   const int n = H * V;
+  if (head_norm) {
+    const long long warps = (long long)n_tokens * H;
+    const unsigned blocks = (unsigned)((warps + 3) / 4);
+    if (out_dtype == AB_F32)
+      ab_launch(linattn_output_head_kernel<float>, dim3(blocks), dim3(128), 0, stream, (const float*)o_raw, proj, ld, off_g,
+                weight, tok_seq, (float*)out, n_tokens, H, V, eps, gate_silu);
+    else if (out_dtype == AB_BF16)
+      ab_launch(linattn_output_head_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, (const float*)o_raw, proj, ld, off_g,
+                weight, tok_seq, (bf16*)out, n_tokens, H, V, eps, gate_silu);
+    else
+      return AB_BAD_ARG;
+    return ab_launch_status();
+  }
   if (n % 4 == 0 && n <= 8192 && ld % 4 == 0 && off_g % 4 == 0 && (out_dtype == AB_F32 || out_dtype == AB_BF16)) {
 #define AB_GO(T, NV) ab_launch(linattn_output_vec_kernel<T, NV>, dim3((unsigned)n_tokens), dim3(256), 0, stream, \
-                               (const float*)o_raw, proj, ld, off_g, weight, tok_seq, (T*)out, n, eps)
+                               (const float*)o_raw, proj, ld, off_g, weight, tok_seq, (T*)out, n, eps, gate_silu)
     if (out_dtype == AB_F32) {
       if (n <= 1024) AB_GO(float, 1); else if (n <= 2048) AB_GO(float, 2); else if (n <= 4096) AB_GO(float, 4); else AB_GO(float, 8);
     } else {
@@ -531,11 +653,25 @@ AB_API int ab_linear_attention_step(const float* proj, int ld, int off_q, int of
   const int threads = n >= 1024 ? 256 : 128;
   if (out_dtype == AB_F32)
     ab_launch(linattn_output_kernel<float>, dim3((unsigned)n_tokens), dim3(threads), 0, stream, (const float*)o_raw, proj,
-              ld, off_g, weight, tok_seq, (float*)out, n, eps);
+              ld, off_g, weight, tok_seq, (float*)out, n, eps, gate_silu);
   else if (out_dtype == AB_BF16)
     ab_launch(linattn_output_kernel<bf16>, dim3((unsigned)n_tokens), dim3(threads), 0, stream, (const float*)o_raw, proj,
-              ld, off_g, weight, tok_seq, (bf16*)out, n, eps);
+              ld, off_g, weight, tok_seq, (bf16*)out, n, eps, gate_silu);
   else
     return AB_BAD_ARG;
   return ab_launch_status();
+}
+
+// The form without options: silu on q, k, v, no rotation, the root mean square over all heads, sigmoid(g).
+AB_API int ab_linear_attention_step(const float* proj, int ld, int off_q, int off_k, int off_v, int off_g,
+                                    const float* decay, float* state, int H, int D, int V, const int* cu_q,
+                                    const int* slots, const int* tok_seq, int n_seqs, int n_tokens, float* o_raw,
+                                    const float* weight, float eps, void* out, int out_dtype, int write_state,
+                                    int stream_from, const int* item_seq, const int* item_t0, const int* item_t1,
+                                    int n_items, float* pieces, const int* seq_first, const int* seq_count,
+                                    cudaStream_t stream) {
+  return ab_linear_attention_step_opts(proj, ld, off_q, off_k, off_v, off_g, decay, state, H, D, V, cu_q, slots, tok_seq,
+                                       n_seqs, n_tokens, o_raw, weight, eps, out, out_dtype, write_state, stream_from,
+                                       item_seq, item_t0, item_t1, n_items, pieces, seq_first, seq_count, 1, nullptr,
+                                       nullptr, 0, 0, nullptr, 1.0f, 0, 0, stream);
 }

@@ -5,6 +5,9 @@
 // chosen; the `top` largest s among those are chosen (the lower index wins a tie); their weights are
 // s / (sum of the chosen s + 1e-20) * scale.
 // Experts: y_t = sum_j weight_j * W_down[e_j] act(W_up[e_j] h_t), act = exact gelu (erf) here.
+// Options: a bias on the router's logits; gated experts, y_t = sum_j weight_j * W_down[e_j] (act(W_gate[e_j] h_t) *
+// (W_up[e_j] h_t)).  (With one group, all groups kept and scale 1 the weights are the softmax over the chosen
+// logits alone: s_j / sum of the chosen s is exp(z_j) / sum of the chosen exp(z).)
 // The pair kernels read each chosen expert's rows once per pair: the form for steps of few tokens, where the
 // weights stream from memory once and every token adds its experts in the order of its choices.
 #include "common.cuh"
@@ -57,7 +60,7 @@ __device__ __forceinline__ float lane_dot(const bf16* __restrict__ a, const floa
 // z[t, e] = W_r[e] . h[t]: one warp per (token, expert)
 template <typename T>
 __global__ void moe_logits_kernel(const T* __restrict__ h, int ld, const float* __restrict__ wr, int n_tokens, int width,
-                                  int E, float* __restrict__ z) {
+                                  int E, float* __restrict__ z, const float* __restrict__ bias) {
   pdl_wait();
   pdl_trigger();
   const int lane = threadIdx.x & 31;
@@ -65,7 +68,7 @@ __global__ void moe_logits_kernel(const T* __restrict__ h, int ld, const float* 
   if (id >= (long long)n_tokens * E) return;
   const int t = (int)(id / E), e = (int)(id - (long long)t * E);
   const float part = warp_sum(lane_dot(h + (size_t)t * ld, wr + (size_t)e * width, width, lane));
-  if (lane == 0) z[id] = part;
+  if (lane == 0) z[id] = part + (bias != nullptr ? bias[e] : 0.f);
 }
 
 // the choice, one warp per token, from the logits z [T, E]
@@ -150,8 +153,10 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int n_tokens, int 
   }
 }
 
-AB_API int ab_moe_route(const void* h, int dtype, int ld, const float* wr, int n_tokens, int width, int E, int groups,
-                        int keep, int top, float scale, float* z, int* idx, float* wts, cudaStream_t stream) {
+// `bias`: float [E] added to the logits, or null
+AB_API int ab_moe_route_bias(const void* h, int dtype, int ld, const float* wr, const float* bias, int n_tokens, int width,
+                             int E, int groups, int keep, int top, float scale, float* z, int* idx, float* wts,
+                             cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
   if (E <= 0 || E > MOE_MAX_EXPERTS || groups <= 0 || E % groups || keep <= 0 || keep > groups || top <= 0 ||
       top > keep * (E / groups))
@@ -160,9 +165,9 @@ AB_API int ab_moe_route(const void* h, int dtype, int ld, const float* wr, int n
   const long long lw = (long long)n_tokens * E;
   const unsigned lblocks = (unsigned)((lw + 7) / 8);
   if (dtype == AB_F32)
-    ab_launch(moe_logits_kernel<float>, dim3(lblocks), dim3(256), 0, stream, (const float*)h, ld, wr, n_tokens, width, E, z);
+    ab_launch(moe_logits_kernel<float>, dim3(lblocks), dim3(256), 0, stream, (const float*)h, ld, wr, n_tokens, width, E, z, bias);
   else if (dtype == AB_BF16)
-    ab_launch(moe_logits_kernel<bf16>, dim3(lblocks), dim3(256), 0, stream, (const bf16*)h, ld, wr, n_tokens, width, E, z);
+    ab_launch(moe_logits_kernel<bf16>, dim3(lblocks), dim3(256), 0, stream, (const bf16*)h, ld, wr, n_tokens, width, E, z, bias);
   else
     return AB_BAD_ARG;
   int rc = ab_launch_status();
@@ -174,13 +179,20 @@ AB_API int ab_moe_route(const void* h, int dtype, int ld, const float* wr, int n
   return ab_launch_status();
 }
 
+AB_API int ab_moe_route(const void* h, int dtype, int ld, const float* wr, int n_tokens, int width, int E, int groups,
+                        int keep, int top, float scale, float* z, int* idx, float* wts, cudaStream_t stream) {
+  return ab_moe_route_bias(h, dtype, ld, wr, nullptr, n_tokens, width, E, groups, keep, top, scale, z, idx, wts, stream);
+}
+
 __device__ __forceinline__ float gelu_erf(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f)); }
 __device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
 
-// act[p, j] = f(W_up[e_p][j] . h[t_p]) for pair p = t * top + k.  One warp per (pair, j).
+// act[p, j] = f(W_up[e_p][j] . h[t_p]) for pair p = t * top + k, or, gated (w_gate given),
+// f(W_gate[e_p][j] . h[t_p]) * (W_up[e_p][j] . h[t_p]).  One warp per (pair, j).
 template <typename T>
-__global__ void moe_up_pairs_kernel(const T* __restrict__ h, int ld, const T* __restrict__ w_up, const int* __restrict__ idx,
-                                    T* __restrict__ act, int n_pairs, int top, int width, int ff, int activation) {
+__global__ void moe_up_pairs_kernel(const T* __restrict__ h, int ld, const T* __restrict__ w_up, const T* __restrict__ w_gate,
+                                    const int* __restrict__ idx, T* __restrict__ act, int n_pairs, int top, int width,
+                                    int ff, int activation) {
   pdl_wait();
   pdl_trigger();
   const int lane = threadIdx.x & 31;
@@ -190,6 +202,11 @@ __global__ void moe_up_pairs_kernel(const T* __restrict__ h, int ld, const T* __
   const int e = idx[p];
   const T* x = h + (size_t)(p / top) * ld;
   const float part = warp_sum(lane_dot(x, w_up + ((size_t)e * ff + j) * width, width, lane));
+  if (w_gate != nullptr) {
+    const float gate = warp_sum(lane_dot(x, w_gate + ((size_t)e * ff + j) * width, width, lane));
+    if (lane == 0) act[(size_t)p * ff + j] = from_f32<T>((activation == 0 ? gelu_erf(gate) : silu(gate)) * part);
+    return;
+  }
   if (lane == 0) {
     act[(size_t)p * ff + j] = from_f32<T>(activation == 0 ? gelu_erf(part) : silu(part));
   }
@@ -216,9 +233,10 @@ __global__ void moe_down_pairs_kernel(const T* __restrict__ act, const T* __rest
   if (lane == 0) out[(size_t)t * width + i] = from_f32<T>(total);
 }
 
-AB_API int ab_moe_pairs(const void* h, int dtype, int ld, const void* w_up, const void* w_down, const int* idx,
-                        const float* wts, void* act, void* out, int n_tokens, int top, int width, int ff, int E,
-                        int activation, cudaStream_t stream) {
+// `w_gate`: [E, ff, width] for gated experts, or null
+AB_API int ab_moe_pairs_gated(const void* h, int dtype, int ld, const void* w_up, const void* w_gate, const void* w_down,
+                              const int* idx, const float* wts, void* act, void* out, int n_tokens, int top, int width,
+                              int ff, int E, int activation, cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
   if (top <= 0 || width <= 0 || ff <= 0 || E <= 0 || (activation != 0 && activation != 1)) return AB_BAD_ARG;
   const int wpb = 8;
@@ -227,12 +245,12 @@ AB_API int ab_moe_pairs(const void* h, int dtype, int ld, const void* w_up, cons
   if (up_blocks > 0x7fffffffLL || down_blocks > 0x7fffffffLL) return AB_BAD_ARG;
   if (dtype == AB_F32) {
     ab_launch(moe_up_pairs_kernel<float>, dim3((unsigned)up_blocks), dim3(wpb * 32), 0, stream, (const float*)h, ld,
-              (const float*)w_up, idx, (float*)act, n_tokens * top, top, width, ff, activation);
+              (const float*)w_up, (const float*)w_gate, idx, (float*)act, n_tokens * top, top, width, ff, activation);
     ab_launch(moe_down_pairs_kernel<float>, dim3((unsigned)down_blocks), dim3(wpb * 32), 0, stream, (const float*)act,
               (const float*)w_down, idx, wts, (float*)out, n_tokens, top, width, ff, E);
   } else if (dtype == AB_BF16) {
     ab_launch(moe_up_pairs_kernel<bf16>, dim3((unsigned)up_blocks), dim3(wpb * 32), 0, stream, (const bf16*)h, ld,
-              (const bf16*)w_up, idx, (bf16*)act, n_tokens * top, top, width, ff, activation);
+              (const bf16*)w_up, (const bf16*)w_gate, idx, (bf16*)act, n_tokens * top, top, width, ff, activation);
     ab_launch(moe_down_pairs_kernel<bf16>, dim3((unsigned)down_blocks), dim3(wpb * 32), 0, stream, (const bf16*)act,
               (const bf16*)w_down, idx, wts, (bf16*)out, n_tokens, top, width, ff, E);
   } else {
@@ -241,12 +259,21 @@ AB_API int ab_moe_pairs(const void* h, int dtype, int ld, const void* w_up, cons
   return ab_launch_status();
 }
 
+AB_API int ab_moe_pairs(const void* h, int dtype, int ld, const void* w_up, const void* w_down, const int* idx,
+                        const float* wts, void* act, void* out, int n_tokens, int top, int width, int ff, int E,
+                        int activation, cudaStream_t stream) {
+  return ab_moe_pairs_gated(h, dtype, ld, w_up, nullptr, w_down, idx, wts, act, out, n_tokens, top, width, ff, E,
+                            activation, stream);
+}
+
 // All experts at once, for steps of many tokens: up[t, e * ff + j] holds W_up[e][j] . h[t] for every expert
 // (one product); in place it becomes act(up) * (the token's weight for expert e, 0 if e was not chosen), so
 // that one product with the experts side by side, [width, E * ff], adds the chosen experts' outputs.
+// Gated: a row of `up` holds the gates of all experts and then their up-projections (2 * E * ff numbers); the result
+// takes the gates' place.
 template <typename T>
 __global__ void moe_weigh_all_kernel(T* __restrict__ up, const int* __restrict__ idx, const float* __restrict__ wts,
-                                     int n_tokens, int top, int ff, int E, int activation) {
+                                     int n_tokens, int top, int ff, int E, int activation, int gated) {
   const int t = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;       // column in [0, E * ff)
   if (c >= E * ff) return;
@@ -254,11 +281,12 @@ __global__ void moe_weigh_all_kernel(T* __restrict__ up, const int* __restrict__
   float g = 0.f;
   for (int k = 0; k < top; ++k)
     if (idx[(size_t)t * top + k] == e) g = wts[(size_t)t * top + k];
-  T* x = up + (size_t)t * E * ff + c;
+  T* x = up + (size_t)t * E * ff * (gated ? 2 : 1) + c;
   float y = 0.f;
   if (g != 0.f) {
     const float z = to_f32(*x);
     y = g * (activation == 0 ? gelu_erf(z) : silu(z));
+    if (gated) y *= to_f32(x[(size_t)E * ff]);
   }
   *x = from_f32<T>(y);
 }
@@ -267,7 +295,7 @@ __global__ void moe_weigh_all_kernel(T* __restrict__ up, const int* __restrict__
 // of experts that were not chosen are written without being read
 __global__ void moe_weigh_all_bf16x8_kernel(bf16* __restrict__ up, const int* __restrict__ idx,
                                             const float* __restrict__ wts, int n_tokens, int top, int ff, int E,
-                                            int activation) {
+                                            int activation, int gated) {
   const int t = blockIdx.y;
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (c >= E * ff) return;
@@ -275,35 +303,48 @@ __global__ void moe_weigh_all_bf16x8_kernel(bf16* __restrict__ up, const int* __
   float g = 0.f;
   for (int k = 0; k < top; ++k)
     if (idx[(size_t)t * top + k] == e) g = wts[(size_t)t * top + k];
-  uint4* x = reinterpret_cast<uint4*>(up + (size_t)t * E * ff + c);
+  uint4* x = reinterpret_cast<uint4*>(up + (size_t)t * E * ff * (gated ? 2 : 1) + c);
   uint4 v = make_uint4(0, 0, 0, 0);
   if (g != 0.f) {
     v = *x;
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (gated) u = *reinterpret_cast<const uint4*>(up + (size_t)t * E * ff * 2 + (size_t)E * ff + c);
     __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+    const __nv_bfloat162* pu = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float2 z = __bfloat1622float2(p[j]);
       z.x = g * (activation == 0 ? gelu_erf(z.x) : silu(z.x));
       z.y = g * (activation == 0 ? gelu_erf(z.y) : silu(z.y));
+      if (gated) {
+        const float2 m = __bfloat1622float2(pu[j]);
+        z.x *= m.x;
+        z.y *= m.y;
+      }
       p[j] = __floats2bfloat162_rn(z.x, z.y);
     }
   }
   *x = v;
 }
 
-AB_API int ab_moe_weigh_all(void* up, int dtype, const int* idx, const float* wts, int n_tokens, int top, int ff, int E,
-                            int activation, cudaStream_t stream) {
+AB_API int ab_moe_weigh_all_gated(void* up, int dtype, const int* idx, const float* wts, int n_tokens, int top, int ff,
+                                  int E, int activation, int gated, cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
   if (top <= 0 || ff <= 0 || E <= 0 || n_tokens > 65535 || (activation != 0 && activation != 1)) return AB_BAD_ARG;
   dim3 grid((unsigned)(((long long)E * ff + 255) / 256), (unsigned)n_tokens);
   if (dtype == AB_F32)
-    moe_weigh_all_kernel<float><<<grid, 256, 0, stream>>>((float*)up, idx, wts, n_tokens, top, ff, E, activation);
+    moe_weigh_all_kernel<float><<<grid, 256, 0, stream>>>((float*)up, idx, wts, n_tokens, top, ff, E, activation, gated);
   else if (dtype == AB_BF16 && ff % 8 == 0 && (((uintptr_t)up) & 15) == 0) {
     dim3 grid8((unsigned)(((long long)E * ff / 8 + 255) / 256), (unsigned)n_tokens);
-    moe_weigh_all_bf16x8_kernel<<<grid8, 256, 0, stream>>>((bf16*)up, idx, wts, n_tokens, top, ff, E, activation);
+    moe_weigh_all_bf16x8_kernel<<<grid8, 256, 0, stream>>>((bf16*)up, idx, wts, n_tokens, top, ff, E, activation, gated);
   } else if (dtype == AB_BF16)
-    moe_weigh_all_kernel<bf16><<<grid, 256, 0, stream>>>((bf16*)up, idx, wts, n_tokens, top, ff, E, activation);
+    moe_weigh_all_kernel<bf16><<<grid, 256, 0, stream>>>((bf16*)up, idx, wts, n_tokens, top, ff, E, activation, gated);
   else
     return AB_BAD_ARG;
   return ab_launch_status();
+}
+
+AB_API int ab_moe_weigh_all(void* up, int dtype, const int* idx, const float* wts, int n_tokens, int top, int ff, int E,
+                            int activation, cudaStream_t stream) {
+  return ab_moe_weigh_all_gated(up, dtype, idx, wts, n_tokens, top, ff, E, activation, 0, stream);
 }

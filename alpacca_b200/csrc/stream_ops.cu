@@ -5,6 +5,10 @@
 //   token_gate     a[t, j] = act(z[t, j]) * table[token_t, off + j]    a product gated by a per-token table row;
 //                  act = gelu_tanh: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 //   add_unit_norm  x[t, :] += y[t, :] / sqrt(mean(y[t, :]^2) + eps) * w[:]
+//   post_norm_add  the same for a sub-layer whose output is normed before it joins the stream, with the next
+//                  sub-layer's norm in the same kernel:  y = a, or y = (unit(a) * wa + unit(b) * wb) / 2 for two
+//                  sub-layers side by side;  x += unit(y) * w;  out = cast(unit(x) * w_next)  (if asked for);
+//                  unit(v) = v / sqrt(mean(v^2) + eps)
 //
 // Arithmetic is 32-bit; rows whose sequence index is negative (padding of a captured step) are left alone by
 // the kernels that write the stream.
@@ -208,5 +212,95 @@ AB_API int ab_add_unit_norm(float* x, const float* y, const float* w, const int*
   }
   const int threads = width >= 2048 ? 256 : 128;
   ab_launch(add_unit_norm_kernel, dim3((unsigned)n_rows), dim3(threads), 0, stream, x, y, w, tok_seq, width, eps);
+  return ab_launch_status();
+}
+
+
+// A block per row; the row of y waits in shared memory between the passes (width floats).  TA: the dtype of a and b.
+template <typename TA, typename TO>
+__global__ void __launch_bounds__(256)
+post_norm_add_kernel(float* __restrict__ x, const TA* __restrict__ a, const TA* __restrict__ b,
+                     const float* __restrict__ wa, const float* __restrict__ wb, const float* __restrict__ w,
+                     const float* __restrict__ w_next, TO* __restrict__ out, const int* __restrict__ tok_seq, int width,
+                     float eps) {
+  extern __shared__ float pn_row[];
+  __shared__ float scratch[32];
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  if (tok_seq != nullptr && tok_seq[t] < 0) {
+    if (out != nullptr)
+      for (int j = threadIdx.x; j < width; j += blockDim.x) out[(size_t)t * width + j] = from_f32<TO>(0.f);
+    return;
+  }
+  const TA* ar = a + (size_t)t * width;
+  const float n = (float)width;
+  float sa = 0.f, sb = 0.f;
+  if (b == nullptr) {
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+      const float v = to_f32(ar[j]);
+      pn_row[j] = v;
+      sa += v * v;
+    }
+    sa = block_sum(sa, scratch);
+  } else {
+    const TA* br = b + (size_t)t * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+      const float u = to_f32(ar[j]), v = to_f32(br[j]);
+      sa += u * u;
+      sb += v * v;
+    }
+    sa = block_sum(sa, scratch);
+    sb = block_sum(sb, scratch);
+    const float ia = 1.0f / sqrtf(sa / n + eps), ib = 1.0f / sqrtf(sb / n + eps);
+    sa = 0.f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+      const float v = 0.5f * (to_f32(ar[j]) * ia * wa[j] + to_f32(br[j]) * ib * wb[j]);
+      pn_row[j] = v;
+      sa += v * v;
+    }
+    sa = block_sum(sa, scratch);
+  }
+  const float inv = 1.0f / sqrtf(sa / n + eps);
+  float* xr = x + (size_t)t * width;
+  float sx = 0.f;
+  for (int j = threadIdx.x; j < width; j += blockDim.x) {      // a thread meets its own elements of the row again
+    const float v = xr[j] + pn_row[j] * inv * w[j];
+    xr[j] = v;
+    pn_row[j] = v;
+    sx += v * v;
+  }
+  if (out == nullptr) return;
+  sx = block_sum(sx, scratch);
+  const float ix = 1.0f / sqrtf(sx / n + eps);
+  TO* o = out + (size_t)t * width;
+  for (int j = threadIdx.x; j < width; j += blockDim.x) o[j] = from_f32<TO>(pn_row[j] * ix * w_next[j]);
+}
+
+// a, b: [n_rows, width] of dtype `in_dtype` (b, wa, wb null: one input); out of dtype `out_dtype` or null.
+AB_API int ab_post_norm_add(float* x, const void* a, const void* b, int in_dtype, const float* wa, const float* wb,
+                            const float* w, const float* w_next, void* out, int out_dtype, const int* tok_seq, int n_rows,
+                            int width, float eps, cudaStream_t stream) {
+  if (n_rows <= 0 || width <= 0) return AB_OK;
+  if (!x || !a || !w || (b && (!wa || !wb)) || (out && !w_next)) return AB_BAD_ARG;
+  const size_t smem = (size_t)width * sizeof(float);
+  if (smem > 200 * 1024) return AB_BAD_ARG;
+  const int threads = width >= 1024 ? 256 : 128;
+#define AB_GO(TA, TO)                                                                                                   \
+  {                                                                                                                     \
+    if (smem > 48 * 1024) {                                                                                             \
+      cudaError_t e = cudaFuncSetAttribute(post_norm_add_kernel<TA, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                           (int)smem);                                                                  \
+      if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                                \
+    }                                                                                                                   \
+    ab_launch(post_norm_add_kernel<TA, TO>, dim3((unsigned)n_rows), dim3(threads), smem, stream, x, (const TA*)a,       \
+              (const TA*)b, wa, wb, w, w_next, (TO*)out, tok_seq, width, eps);                                          \
+  }
+  const bool out_f32 = out == nullptr || out_dtype == AB_F32;
+  if (!out_f32 && out_dtype != AB_BF16) return AB_BAD_ARG;
+  if (in_dtype == AB_F32) { if (out_f32) AB_GO(float, float) else AB_GO(float, bf16) }
+  else if (in_dtype == AB_BF16) { if (out_f32) AB_GO(bf16, float) else AB_GO(bf16, bf16) }
+  else return AB_BAD_ARG;
+#undef AB_GO
   return ab_launch_status();
 }

@@ -1125,10 +1125,14 @@ def latent_attention(q, out, cache, ctx, H, C, R, scale, sink=None):
 MOE_ACTIVATIONS = {"gelu": 0, "silu": 1}
 
 
-def moe_route(h, router, n_tokens, groups, keep, top, scale):
+def moe_route(h, router, n_tokens, groups, keep, top, scale, bias=None):
     """(experts int32 [T, top], weights float32 [T, top]) of every token: softmax over all experts, the `keep`
-    best of `groups` groups of neighbours, the `top` best experts of those, weights renormalised times `scale`."""
-    _cuda(h, router)
+    best of `groups` groups of neighbours, the `top` best experts of those, weights renormalised times `scale`.
+    `bias` float32 [E] is added to the logits.  (One group, scale 1: the softmax over the chosen logits alone.)"""
+    _cuda(h, router, bias)
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == router.shape[0],
+              "moe_route: bias float32 [experts]")
     E, width = router.shape
     _need(router.dtype == torch.float32 and router.is_contiguous(), "the router's matrix must be float32")
     _need(h.is_contiguous() and h.shape[-1] == width and h.numel() >= n_tokens * width, "moe_route: h [T, width]")
@@ -1137,8 +1141,9 @@ def moe_route(h, router, n_tokens, groups, keep, top, scale):
     idx = torch.empty((max(n_tokens, 1), top), dtype=torch.int32, device=h.device)
     wts = torch.empty((max(n_tokens, 1), top), dtype=torch.float32, device=h.device)
     z = torch.empty((max(n_tokens, 1), E), dtype=torch.float32, device=h.device)
-    _check(_lib("moe").ab_moe_route(_p(h), _dt(h), width, _p(router), n_tokens, width, E, groups, keep, top,
-                                    ctypes.c_float(scale), _p(z), _p(idx), _p(wts), _stream()), "moe_route", kernels=2)
+    _check(_lib("moe").ab_moe_route_bias(_p(h), _dt(h), width, _p(router), _p(bias), n_tokens, width, E, groups, keep,
+                                         top, ctypes.c_float(scale), _p(z), _p(idx), _p(wts), _stream()),
+           "moe_route", kernels=2)
     return idx, wts
 
 
@@ -1147,11 +1152,16 @@ MOE_ALL_EXPERTS_MIN_ROWS = 33      # from here a bfloat16 step runs every expert
 #                                    the chosen experts' rows once per (token, expert) pair
 
 
-def moe_experts(h, w_up, w_down, idx, wts, out, n_tokens, activation="gelu"):
+def moe_experts(h, w_up, w_down, idx, wts, out, n_tokens, activation="gelu", gate_up=None):
     """out[t] = sum_j wts[t, j] * W_down[idx[t, j]] @ act(W_up[idx[t, j]] @ h[t]); w_up [E, ff, width],
-    w_down [width, E, ff] (the experts side by side), all of h's dtype."""
-    _cuda(h, w_up, w_down, idx, wts, out)
+    w_down [width, E, ff] (the experts side by side), all of h's dtype.  Gated experts: `gate_up` [2, E, ff, width]
+    holds the gates' matrices and then the up-projections (`w_up` is then gate_up[1]), and an expert is
+    W_down (act(W_gate h) * (W_up h))."""
+    _cuda(h, w_up, w_down, idx, wts, out, gate_up)
     E, ff, width = w_up.shape
+    if gate_up is not None:
+        _need(tuple(gate_up.shape) == (2, E, ff, width) and gate_up.is_contiguous() and gate_up.dtype == h.dtype
+              and w_up.data_ptr() == gate_up[1].data_ptr(), "moe_experts: gate_up [2, E, ff, width] with w_up its second half")
     top = idx.shape[-1]
     _need(tuple(w_down.shape) == (width, E, ff) and w_up.is_contiguous() and w_down.is_contiguous()
           and w_up.dtype == h.dtype and w_down.dtype == h.dtype, "moe_experts: w_up [E, ff, width], w_down [width, E, ff]")
@@ -1160,18 +1170,21 @@ def moe_experts(h, w_up, w_down, idx, wts, out, n_tokens, activation="gelu"):
     _i32(idx, n_tokens * top, "experts")
     _need(wts.dtype == torch.float32 and wts.is_contiguous() and wts.numel() >= n_tokens * top, "weights float32 [T, top]")
     if h.dtype == torch.bfloat16 and MOE_ALL_EXPERTS_MIN_ROWS <= n_tokens <= 65535:
-        up = torch.empty((n_tokens, E * ff), dtype=h.dtype, device=h.device)
-        torch.mm(h[:n_tokens], w_up.view(E * ff, width).t(), out=up)
+        first = w_up if gate_up is None else gate_up
+        cols = first.numel() // width                      # E * ff, or twice that: the gates, then the up-projections
+        up = torch.empty((n_tokens, cols), dtype=h.dtype, device=h.device)
+        torch.mm(h[:n_tokens], first.view(cols, width).t(), out=up)
         _mark("library product")
-        _check(_lib("moe").ab_moe_weigh_all(_p(up), _dt(up), _p(idx), _p(wts), n_tokens, top, ff, E,
-                                            MOE_ACTIVATIONS[activation], _stream()), "moe_weigh_all")
-        torch.mm(up, w_down.view(width, E * ff).t(), out=out[:n_tokens])
+        _check(_lib("moe").ab_moe_weigh_all_gated(_p(up), _dt(up), _p(idx), _p(wts), n_tokens, top, ff, E,
+                                                  MOE_ACTIVATIONS[activation], 0 if gate_up is None else 1, _stream()),
+               "moe_weigh_all")
+        torch.mm(up[:, :E * ff], w_down.view(width, E * ff).t(), out=out[:n_tokens])
         _mark("library product")
         return out
     act = torch.empty((max(n_tokens, 1) * top, ff), dtype=h.dtype, device=h.device)
-    _check(_lib("moe").ab_moe_pairs(_p(h), _dt(h), width, _p(w_up), _p(w_down), _p(idx), _p(wts), _p(act), _p(out),
-                                    n_tokens, top, width, ff, E, MOE_ACTIVATIONS[activation], _stream()), "moe_experts",
-           kernels=2)
+    _check(_lib("moe").ab_moe_pairs_gated(_p(h), _dt(h), width, _p(w_up), _p(gate_up), _p(w_down), _p(idx), _p(wts),
+                                          _p(act), _p(out), n_tokens, top, width, ff, E, MOE_ACTIVATIONS[activation],
+                                          _stream()), "moe_experts", kernels=2)
     return out
 
 
@@ -1241,15 +1254,30 @@ def _linear_attention_pieces(ctx, H, D, V, device):
     return plan
 
 
-def linear_attention_step(proj, offsets, decay, state, ctx, H, D, V, norm_weight, eps, out, write_state=True):
+def linear_attention_step(proj, offsets, decay, state, ctx, H, D, V, norm_weight, eps, out, write_state=True,
+                          activation=True, rot=None, k_scale=1.0, head_norm=False, gate="sigmoid"):
     """Linear attention with a fixed decay per head over the step's tokens, from each sequence's state to its
     new state (csrc/linear_attention.cu).
 
     proj float32 [T, N]: one row per token with zq | zk | zv | g at `offsets` (four column offsets, before the
     activation); decay float32 [H]; state float32 [slots, H, D, V]; out [T, H*V] of the activation dtype gets
     o / rms(o over all heads) * norm_weight * sigmoid(g).  `proj` is scratch: a long step leaves the activations
-    in it."""
-    _cuda(proj, decay, state, norm_weight, out)
+    in it.
+
+    `activation` off: q, k, v enter as projected (on: silu).  `rot` = (cos, sin, n_rot, pairing): q and k are rotated
+    by position.  `k_scale` multiplies k after the rotation.  `head_norm`: the root mean square is taken per head
+    (`norm_weight` may then be None: no weight).  `gate`: "sigmoid" or "silu" of g."""
+    cos, sin, n_rot, pairing = rot if rot is not None else (None, None, 0, 0)
+    _cuda(proj, decay, state, norm_weight, out, cos, sin)
+    _need(gate in ("sigmoid", "silu"), f"linear_attention_step: gate {gate!r} is not sigmoid or silu")
+    _need(norm_weight is not None or head_norm, "linear_attention_step: the norm over all heads needs a weight")
+    if cos is not None:
+        _need(sin is not None and cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous()
+              and sin.is_contiguous() and cos.shape == sin.shape and cos.shape[-1] == n_rot // 2 and n_rot % 2 == 0
+              and 0 < n_rot <= D, "linear_attention_step: rope tables float32 [P, n_rot/2], n_rot even and at most D")
+        _need(ctx.max_kv_len <= cos.shape[0],
+              f"rope tables hold {cos.shape[0]} positions, the step reaches position {ctx.max_kv_len}")
+        _i32(ctx.tok_pos, ctx.n_tokens, "tok_pos")
     T, B = ctx.n_tokens, ctx.n_seqs
     off_q, off_k, off_v, off_g = (int(o) for o in offsets)
     ld = proj.shape[-1]
@@ -1263,8 +1291,8 @@ def linear_attention_step(proj, offsets, decay, state, ctx, H, D, V, norm_weight
           f"linear_attention_step: state must be contiguous float32 [slots, {H}, {D}, {V}]")
     _need(decay.dtype == torch.float32 and decay.numel() == H and decay.is_contiguous(),
           "linear_attention_step: decay float32 [H]")
-    _need(norm_weight.dtype == torch.float32 and norm_weight.numel() == H * V and norm_weight.is_contiguous(),
-          "linear_attention_step: norm weight float32 [H*V]")
+    _need(norm_weight is None or (norm_weight.dtype == torch.float32 and norm_weight.numel() == H * V
+                                  and norm_weight.is_contiguous()), "linear_attention_step: norm weight float32 [H*V]")
     _need(out.is_contiguous() and out.shape[-1] == H * V and out.numel() >= T * H * V,
           "linear_attention_step: out [T, H*V]")
     _i32(ctx.cu_q, B + 1, "cu_q")
@@ -1275,12 +1303,15 @@ def linear_attention_step(proj, offsets, decay, state, ctx, H, D, V, norm_weight
     plan = _linear_attention_pieces(ctx, H, D, V, proj.device) if long_step else None
     item_seq, item_t0, item_t1, n_items, seq_first, seq_count = plan if plan is not None else (None,) * 3 + (0, None, None)
     pieces = torch.empty((n_items, H, D, V), dtype=torch.float32, device=proj.device) if n_items else None
-    _check(_lib("linear_attention").ab_linear_attention_step(
+    plain_qk = cos is None and k_scale == 1.0
+    _check(_lib("linear_attention").ab_linear_attention_step_opts(
         _p(proj), ld, off_q, off_k, off_v, off_g, _p(decay), _p(state), H, D, V, _p(ctx.cu_q), _p(ctx.slots),
         _p(ctx.tok_seq), B, T, _p(o_raw), _p(norm_weight), ctypes.c_float(eps), _p(out), _dt(out),
         1 if write_state else 0, LINEAR_ATTENTION_STREAM_FROM, _p(item_seq), _p(item_t0), _p(item_t1), n_items,
-        _p(pieces), _p(seq_first), _p(seq_count), _stream()), "linear_attention_step",
-        kernels=(5 if n_items else 3) if long_step else 2)
+        _p(pieces), _p(seq_first), _p(seq_count), 1 if activation else 0, _p(cos), _p(sin), int(n_rot), int(pairing),
+        _p(ctx.tok_pos) if cos is not None else None, ctypes.c_float(k_scale), 1 if head_norm else 0,
+        1 if gate == "silu" else 0, _stream()), "linear_attention_step",
+        kernels=((4 if n_items else 2) + (1 if activation else 0) + (0 if plain_qk else 1)) if long_step else 2)
     return out
 
 
@@ -1288,7 +1319,7 @@ ATTENTION_MAPS_MAX_DIM = 256
 
 
 def attention_prepare(buf, offsets, H, G, M, Dk, Dv, cache, ctx, q_weight=None, k_weight=None, eps=0.0, rot=None,
-                      write_cache=True, bias=None):
+                      write_cache=True, bias=None, v_norm=False, v_side_by_side=False):
     """Query and key norm, position rotation and the append of keys and values to the cache, for an attention
     whose heads have M score maps (csrc/attention_maps.cu).
 
@@ -1296,7 +1327,9 @@ def attention_prepare(buf, offsets, H, G, M, Dk, Dv, cache, ctx, q_weight=None, 
     vectors of Dv at offsets[2] (which may be the keys' own place: values that are the keys as projected).
     The queries are rewritten in place; keys and values go to `cache` (a KVLayerView whose key pages are
     [n_pages, G*M, page, Dk] and value pages [n_pages, G, page, Dv]).  `bias` float32 [N]: the projection's
-    bias where the product left it out; it is added first."""
+    bias where the product left it out; it is added first.  `v_norm`: every value vector is divided by its root mean
+    square (eps inside the root) before it is stored.  `v_side_by_side`: the value pages are [n_pages, 1, page,
+    G*Dv], a token's value heads in one row."""
     k_pages, v_pages, table = cache.k, cache.v, cache.block_table
     cos, sin, n_rot, pairing = rot if rot is not None else (None, None, 0, 0)
     _cuda(buf, k_pages, v_pages, table, q_weight, k_weight, cos, sin)
@@ -1311,7 +1344,8 @@ def attention_prepare(buf, offsets, H, G, M, Dk, Dv, cache, ctx, q_weight=None, 
     page = k_pages.shape[2]
     _need(k_pages.dtype == buf.dtype and v_pages is not None and v_pages.dtype == buf.dtype and k_pages.is_contiguous()
           and v_pages.is_contiguous() and tuple(k_pages.shape[1:]) == (G * M, page, Dk)
-          and tuple(v_pages.shape[1:]) == (G, page, Dv) and v_pages.shape[0] == k_pages.shape[0],
+          and tuple(v_pages.shape[1:]) == ((1, page, G * Dv) if v_side_by_side else (G, page, Dv))
+          and v_pages.shape[0] == k_pages.shape[0],
           f"attention_prepare: cache pages [n, {G * M}, page, {Dk}] and [n, {G}, page, {Dv}] of buf's dtype")
     _need(table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
           and ctx.max_kv_len <= table.shape[1] * page, "attention_prepare: the block table does not cover the step")
@@ -1331,11 +1365,11 @@ def attention_prepare(buf, offsets, H, G, M, Dk, Dv, cache, ctx, q_weight=None, 
               "attention_prepare: bias float32 [N]")
     _i32(ctx.tok_pos, T, "tok_pos")
     _i32(ctx.tok_seq, T, "tok_seq")
-    _check(_lib("attention_maps").ab_attention_prepare(
+    _check(_lib("attention_maps").ab_attention_prepare_opts(
         _p(buf), _dt(buf), N, off_q, off_k, off_v, H * M, G * M, G, Dk, Dv, _p(q_weight), _p(k_weight),
         ctypes.c_float(eps), _p(cos), _p(sin), n_rot, pairing, _p(ctx.tok_pos), _p(ctx.tok_seq), _p(table),
-        table.shape[1], _p(k_pages), _p(v_pages), page, T, 1 if write_cache else 0, _p(bias), _stream()),
-        "attention_prepare")
+        table.shape[1], _p(k_pages), _p(v_pages), page, T, 1 if write_cache else 0, _p(bias), 1 if v_norm else 0,
+        1 if v_side_by_side else 0, _stream()), "attention_prepare")
 
 
 def attention_maps(q, q_stride, out, cache, ctx, H, G, M, Dk, Dv, scale, window=0, sink=None, coef=0.0,
@@ -1513,3 +1547,101 @@ def add_unit_norm(residual, y, weight, eps, ctx):
     _check(_lib("stream_ops").ab_add_unit_norm(_p(residual), _p(y), _p(weight), _p(ctx.tok_seq), T, E,
                                                ctypes.c_float(eps), _stream()), "add_unit_norm")
     return residual
+
+
+# ---------------------------------------------------------------------------
+# attention whose softmax weights are mixed across heads; sub-layers whose output is normed before it joins the stream
+
+def talk_max_row() -> int:
+    """The most numbers G*Dv of a token's values that `attention_talk` takes."""
+    return 2048
+
+
+TALK_ON_TENSOR_CORES = True      # bfloat16 steps whose sizes the tile kernel takes run there
+
+
+def attention_talk(q, q_stride, out, cache, ctx, H, G, Dk, Dv, scale, talk, gate_rows=None, gate_stride=0, window=0):
+    """Attention over the cached keys and values with the softmax weights mixed across heads:
+    out[t, h] = gate * sum_g talk[h, g] * (weights of head g applied to the values of h's key/value head).
+
+    q: the prepared rows, query vector x of a token at x*Dk, ordered so that vector x reads key head x % G (head
+    g = (x % G) * (H/G) + x / G); cache: key pages [n, G, page, Dk], value pages [n, 1, page, G*Dv] (the heads of a
+    token side by side); talk float32 [H, H]; gate_rows (or None): rows of `gate_stride` numbers of q's dtype whose
+    first H*Dv are the gate's logits (sigmoid is applied); out [T, H*Dv] of q's dtype, heads in their own order.
+    Every head's attention over all value heads is one float32 row A[t, x, G*Dv]; the mixing is a second kernel.
+    In bfloat16 with sizes in steps of 16 and G*Dv up to 256 the first is the tensor-core tile kernel."""
+    k_pages, v_pages, table = cache.k, cache.v, cache.block_table
+    _cuda(q, out, k_pages, v_pages, table, talk, gate_rows)
+    T, W = ctx.n_tokens, G * Dv
+    page = k_pages.shape[2]
+    _need(H % G == 0 and 0 < Dk <= ATTENTION_MAPS_MAX_DIM and 0 < W <= talk_max_row(),
+          f"attention_talk: {H}/{G} heads of {Dk} and {Dv} dims not supported (G*Dv up to {talk_max_row()})")
+    _need(q.is_contiguous() and out.is_contiguous() and out.dtype == q.dtype and k_pages.dtype == q.dtype
+          and v_pages.dtype == q.dtype and q.numel() >= T * q_stride and q_stride >= H * Dk
+          and out.shape[-1] == H * Dv and out.numel() >= T * H * Dv,
+          "attention_talk: q [T, stride], out [T, H*Dv] and the cache share one dtype")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and tuple(k_pages.shape[1:]) == (G, page, Dk)
+          and tuple(v_pages.shape[1:]) == (1, page, W) and k_pages.shape[0] == v_pages.shape[0],
+          "attention_talk: cache pages [n, G, page, Dk] and [n, 1, page, G*Dv]")
+    _need(table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+          and ctx.max_kv_len <= table.shape[1] * page, "attention_talk: the block table does not cover the step")
+    _need(talk.dtype == torch.float32 and talk.is_contiguous() and tuple(talk.shape) == (H, H),
+          "attention_talk: talk float32 [H, H]")
+    if gate_rows is not None:
+        _need(gate_rows.dtype == q.dtype and gate_rows.is_contiguous() and gate_stride >= H * Dv
+              and gate_rows.numel() >= (T - 1) * gate_stride + H * Dv, "attention_talk: gate rows of q's dtype")
+    _i32(ctx.tok_pos, T, "tok_pos")
+    _i32(ctx.tok_seq, T, "tok_seq")
+    A = torch.empty((q.shape[0], H * W), dtype=torch.float32, device=q.device)
+    if (TALK_ON_TENSOR_CORES and page == 64
+            and attention_maps_mma_supports(H // G, 1, G, Dk, W, q_stride, q.dtype) and H // G <= 64):
+        # the tile kernel with the G key heads as the maps of one group whose value row is all heads' values
+        _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
+        if ctx.is_decode:
+            tile_seq = tile_q0 = _row_index(q.device, T)
+            n_tiles, tpt = T, 1
+        else:
+            tile_seq, tile_q0, n_tiles, tpt = _prefill_tiles(ctx, H // G, q.device)
+        _check(_lib("attention_mma").ab_attention_prefill_maps_bf16(
+            _p(q), q_stride, _p(A), 1, _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_pos),
+            _p(ctx.cu_q), _p(ctx.tok_seq), _p(tile_seq), _p(tile_q0), n_tiles, tpt, H, G, G, Dk, W,
+            ctypes.c_float(scale), int(window or 0), None, _stream()), "attention_prefill")
+    else:
+        _check(_lib("attention_maps").ab_talk_attend(
+            _p(q), q_stride, _p(A), _dt(q), _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_pos),
+            _p(ctx.tok_seq), T, H, G, Dk, Dv, page, ctypes.c_float(scale), int(window or 0), _stream()), "talk_attend")
+    _check(_lib("attention_maps").ab_talk_combine(
+        _p(A), _p(talk), _p(gate_rows), int(gate_stride), _p(out), _dt(out), _p(ctx.tok_seq), T, H, G, Dv, _stream()),
+        "talk_combine")
+    return out
+
+
+def post_norm_add(residual, a, weight, eps, ctx=None, b=None, wa=None, wb=None, next_weight=None, out=None,
+                  n_rows=None):
+    """residual[t] += unit(y[t]) * weight with y = a, or y = (unit(a) * wa + unit(b) * wb) / 2 for two sub-layers side
+    by side; then, if `out` is given, out[t] = unit(residual[t]) * next_weight in out's dtype.  unit(v) = v /
+    sqrt(mean(v^2) + eps), 32-bit.  a, b [T, E] float32 or bfloat16; the weights float32 [E]."""
+    _cuda(residual, a, b, weight, wa, wb, next_weight, out)
+    E = residual.shape[-1]
+    T = (ctx.n_tokens if ctx is not None else residual.numel() // E) if n_rows is None else n_rows
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and residual.numel() >= T * E,
+          "post_norm_add: residual float32 [T, E]")
+    for t in (a, b):
+        if t is not None:
+            _need(t.is_contiguous() and t.shape[-1] == E and t.numel() >= T * E and t.dtype == a.dtype,
+                  "post_norm_add: a and b [T, E] of one dtype")
+    for w in (weight, wa, wb, next_weight):
+        if w is not None:
+            _need(w.dtype == torch.float32 and w.is_contiguous() and w.numel() == E, "post_norm_add: weights float32 [E]")
+    _need((b is None) == (wa is None) == (wb is None), "post_norm_add: b comes with wa and wb")
+    _need(E * 4 <= 200 * 1024, f"post_norm_add: rows of {E} numbers do not fit shared memory")
+    if out is not None:
+        _need(next_weight is not None and out.is_contiguous() and out.shape[-1] == E and out.numel() >= T * E,
+              "post_norm_add: out [T, E] comes with next_weight")
+    tok_seq = ctx.tok_seq if ctx is not None else None
+    if tok_seq is not None:
+        _i32(tok_seq, T, "tok_seq")
+    _check(_lib("stream_ops").ab_post_norm_add(
+        _p(residual), _p(a), _p(b), _dt(a), _p(wa), _p(wb), _p(weight), _p(next_weight), _p(out),
+        _dt(out) if out is not None else 0, _p(tok_seq), T, E, ctypes.c_float(eps), _stream()), "post_norm_add")
+    return out

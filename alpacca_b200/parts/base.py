@@ -98,6 +98,17 @@ class OwedNorm:
         return self.x.device
 
 
+@dataclass
+class HalfSum:
+    """What two mixers side by side hand to the block: (unit(a) * wa + unit(b) * wb) / 2, not formed yet; unit(v) =
+    v / sqrt(mean(v^2) + eps).  The block's kernel that adds a sub-layer's output to the stream forms it."""
+    a: torch.Tensor
+    b: torch.Tensor
+    wa: torch.Tensor
+    wb: torch.Tensor
+    eps: float
+
+
 class Part:
     """Base of all parts: parameters by checkpoint name, loading, sub-parts."""
 

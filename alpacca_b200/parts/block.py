@@ -15,7 +15,7 @@ from dataclasses import dataclass
 import torch
 
 from .. import ops
-from .base import Block, FeedForward, Mixer, Norm, OwedNorm
+from .base import Block, FeedForward, HalfSum, Mixer, Norm, OwedNorm
 
 
 @dataclass
@@ -75,6 +75,55 @@ class ParallelBlock(Block):
             return
         ops.residual_add(stream.residual, stream.delta, n_rows=ctx.n_tokens)
         stream.delta = self.ffn.forward(h, ctx)
+
+
+class SandwichBlock(Block):
+    """A norm before AND after each sub-layer: x += Post1(Mixer(Norm1(x))); x += Post2(FeedForward(Norm2(x))).
+
+    The norm after a sub-layer acts on the sub-layer's output alone, so that output cannot wait to be added by
+    the next norm's kernel as it is: one kernel norms it, adds it to the float32 stream and, between the two
+    sub-layers, leaves the next norm's output as well (`ops.post_norm_add`).  A mixer may return a `HalfSum`
+    (two mixers side by side whose normed outputs are averaged); the same kernel forms it.  The norms are
+    `RMSNorm`s (weight per column, eps), 32-bit arithmetic."""
+
+    def __init__(self, norm1: Norm, mixer: Mixer, post1: Norm, norm2: Norm | None = None,
+                 ffn: FeedForward | None = None, post2: Norm | None = None):
+        if (ffn is None) != (norm2 is None) or (ffn is None) != (post2 is None):
+            raise ValueError("a feed-forward comes with a norm before and a norm after it")
+        self.norm1, self.mixer, self.post1 = norm1, mixer, post1
+        self.norm2, self.ffn, self.post2 = norm2, ffn, post2
+
+    def cache_specs(self) -> list:
+        several = getattr(self.mixer, "cache_specs", None)      # mixers side by side: an entry for each
+        if several is not None:
+            return several()
+        return super().cache_specs()
+
+    def forward(self, stream: HiddenStream, ctx, cache, write_cache: bool = True) -> None:
+        stream.next_norm = None
+        h = _normed(self.norm1, stream)
+        stream.delta = None
+        y = self.mixer.forward(h, ctx, cache, write_cache)
+        if self.ffn is None:
+            _post_add(self.post1, stream.residual, y, ctx)
+            return
+        h = _post_add(self.post1, stream.residual, y, ctx, then=self.norm2)
+        _post_add(self.post2, stream.residual, self.ffn.forward(h, ctx), ctx)
+
+
+def _post_add(post: Norm, residual, y, ctx, then: Norm | None = None):
+    """residual += post(y); returns then(residual) in the activation dtype where `then` is given."""
+    out = None
+    if then is not None:
+        out = torch.empty((residual.shape[0], residual.shape[-1]), dtype=then.opts.dtype, device=residual.device)
+    more = {}
+    if isinstance(y, HalfSum):
+        more = {"b": y.b, "wa": y.wa, "wb": y.wb}
+        if y.eps != post.eps:
+            raise ValueError("the norms of a sum of two mixers and the norm after it share one eps")
+        y = y.a
+    return ops.post_norm_add(residual, y, post.weight, post.eps, ctx, next_weight=then.weight if then else None,
+                             out=out, **more)
 
 
 def _accepts(part, n_rows: int) -> bool:

@@ -13,10 +13,13 @@ from .linear import Linear
 
 
 class TokenEmbedding(Part):
-    def __init__(self, opts: BuildOptions, vocab: int, width: int, name: str, weight_suffix: str = ".weight"):
+    def __init__(self, opts: BuildOptions, vocab: int, width: int, name: str, weight_suffix: str = ".weight",
+                 norm=None):
+        """`norm`: a norm that the embedded rows pass before they become the stream (32-bit)."""
         self.opts, self.vocab, self.width, self.name = opts, int(vocab), int(width), name
         self.weight_suffix = weight_suffix
         self.weight = None
+        self.norm = norm
 
     def own_param_specs(self):
         return [ParamSpec(f"{self.name}{self.weight_suffix}", (self.vocab, self.width), "matrix", "normal")]
@@ -26,7 +29,10 @@ class TokenEmbedding(Part):
 
     def forward(self, tokens: torch.Tensor, n_rows: int) -> torch.Tensor:
         out = torch.empty((n_rows, self.width), dtype=torch.float32, device=tokens.device)
-        return ops.embed_rows(self.weight, tokens[:n_rows], out)
+        ops.embed_rows(self.weight, tokens[:n_rows], out)
+        if self.norm is None:
+            return out
+        return ops.add_rmsnorm(out, None, self.norm.weight, self.norm.eps, torch.empty_like(out), n_rows=n_rows)
 
 
 class VocabHead(Part):

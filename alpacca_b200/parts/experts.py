@@ -6,6 +6,11 @@
     weights = chosen s / (their sum + 1e-20) * scale;  output = sum of weight * expert(h)
     expert(h) = W_down act(W_up h), no biases
 
+Options: `router_bias` (a bias on the logits, tensor `<router>.b`); `gate_name`: gated experts,
+expert(h) = W_down (act(W_gate h) * (W_up h)).  With one group, all of it kept and scale 1 the weights are the
+softmax over the chosen logits alone (exp(z_j) / sum over the chosen of exp(z)), which is the router of designs that
+choose by logit.
+
 The experts' matrices are stacked ([experts, ff, width] and, side by side, [width, experts, ff]) so that a
 kernel picks an expert by index from device memory: routing never reaches the host, and a step with routed
 experts is captured in a CUDA graph like any other (csrc/moe.cu).  Steps of few tokens read the chosen
@@ -24,7 +29,7 @@ from .base import BuildOptions, FeedForward
 class RoutedExperts(FeedForward):
     def __init__(self, opts: BuildOptions, width: int, inner: int, n_experts: int, top: int, groups: int, keep: int,
                  scale: float, prefix: str, activation: str = "gelu", router_name: str = "router",
-                 expert_names=("e{}.up", "e{}.down")):
+                 expert_names=("e{}.up", "e{}.down"), router_bias: bool = False, gate_name: str | None = None):
         if activation not in ops.MOE_ACTIVATIONS:
             raise ValueError(f"activation must be one of {tuple(ops.MOE_ACTIVATIONS)}, got {activation!r}")
         if n_experts % groups or not 0 < keep <= groups or not 0 < top <= keep * (n_experts // groups):
@@ -32,7 +37,8 @@ class RoutedExperts(FeedForward):
         self.opts, self.width, self.inner, self.E = opts, int(width), int(inner), int(n_experts)
         self.top, self.groups, self.keep, self.scale = int(top), int(groups), int(keep), float(scale)
         self.prefix, self.activation, self.router_name, self.expert_names = prefix, activation, router_name, expert_names
-        self.router = self.w_up = self.w_down = None
+        self.router_bias, self.gate_name = bool(router_bias), gate_name
+        self.router = self.bias = self.w_up = self.w_down = self.w_gate_up = None
 
     def own_param_specs(self):
         up, down = self.expert_names
@@ -40,16 +46,29 @@ class RoutedExperts(FeedForward):
         for e in range(self.E):
             specs.append(ParamSpec(f"{self.prefix}.{up.format(e)}", (self.inner, self.width), "matrix", "normal"))
             specs.append(ParamSpec(f"{self.prefix}.{down.format(e)}", (self.width, self.inner), "matrix", "normal"))
+        if self.gate_name is not None:
+            specs += [ParamSpec(f"{self.prefix}.{self.gate_name.format(e)}", (self.inner, self.width), "matrix", "normal")
+                      for e in range(self.E)]
+        if self.router_bias:
+            specs.append(ParamSpec(f"{self.prefix}.{self.router_name}.b", (self.E,), "vector", "normal"))
         return specs
 
     def load_own(self, fetch):
         specs = self.own_param_specs()
         self.router = fetch(specs[0])
-        self.w_up = torch.stack([fetch(s) for s in specs[1::2]]).contiguous()
-        self.w_down = torch.stack([fetch(s) for s in specs[2::2]], dim=1).contiguous()      # [width, E, ff]
+        ups = [fetch(s) for s in specs[1:1 + 2 * self.E:2]]
+        self.w_down = torch.stack([fetch(s) for s in specs[2:2 + 2 * self.E:2]], dim=1).contiguous()      # [width, E, ff]
+        if self.gate_name is not None:
+            gates = [fetch(s) for s in specs[1 + 2 * self.E:1 + 3 * self.E]]
+            self.w_gate_up = torch.stack([torch.stack(gates), torch.stack(ups)]).contiguous()      # [2, E, ff, width]
+            self.w_up = self.w_gate_up[1]
+        else:
+            self.w_up = torch.stack(ups).contiguous()
+        if self.router_bias:
+            self.bias = fetch(specs[-1])
 
     def forward(self, h, ctx):
         T = ctx.n_tokens
-        idx, wts = ops.moe_route(h, self.router, T, self.groups, self.keep, self.top, self.scale)
+        idx, wts = ops.moe_route(h, self.router, T, self.groups, self.keep, self.top, self.scale, bias=self.bias)
         out = torch.empty((h.shape[0], self.width), dtype=h.dtype, device=h.device)
-        return ops.moe_experts(h, self.w_up, self.w_down, idx, wts, out, T, self.activation)
+        return ops.moe_experts(h, self.w_up, self.w_down, idx, wts, out, T, self.activation, gate_up=self.w_gate_up)

@@ -17,6 +17,16 @@ Options, each a constructor argument:
                      learned vectors of size `dim`; o is then divided by its root mean square over `vdim` (no
                      weight) and multiplied by 1 - d.  (Ye et al., "Differential Transformer".)
 
+    qk_norm_weight   off: the query/key norm has no weight (and no tensors)
+    value_norm       every value vector is divided by its root mean square over `vdim` (no weight) before it is cached
+    head_mix         a matrix T [H, H] (tensor `<prefix>.<head_mix>`) mixes the softmax weights of all heads before they
+                     meet the values: w'_h = sum_g T[h, g] w_g, and head h applies w'_h to the values of its own
+                     key/value head (Shazeer et al., "Talking-Heads Attention", mix after the softmax like this).
+                     One map, no sink.  The cache keeps a token's value heads side by side in one row, head g's
+                     attention over that whole row is computed once, and o_h = sum_g T[h, g] A[g, group of h]; the
+                     rows of W_q are reordered at load so that neighbouring query vectors read different key heads.
+    gate             the concatenated heads are multiplied by sigmoid(W_g h) (tensor `<prefix>.<gate>`) before W_o
+
 The rotation turns the first n_rot dims of every query and key vector (each map by itself).  In bfloat16 with key
 and value sizes in steps of 16, prompts and decode steps run on the tensor-core kernels of csrc/attention_mma.cu
 (several maps leave their outputs in float32, which one more kernel combines); everything else runs
@@ -39,7 +49,8 @@ class MapsAttention(Mixer):
                  position: PositionEncoding | None, prefix: str, scale: float, eps: float, window: int | None = None,
                  n_maps: int = 1, bias: bool = False, qk_norm: bool = False, values_are_keys: bool = False,
                  sink: bool = False, difference: float | None = None, names=("q", "k", "v", "o"),
-                 weight_suffix: str = "", bias_suffix: str = ".b", out_dtype=None):
+                 weight_suffix: str = "", bias_suffix: str = ".b", out_dtype=None, qk_norm_weight: bool = True,
+                 value_norm: bool = False, head_mix: str | None = None, gate: str | None = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{prefix}: {n_heads} heads cannot share {n_kv_heads} key/value heads")
         self.opts, self.prefix = opts, prefix
@@ -55,6 +66,14 @@ class MapsAttention(Mixer):
         big = ops.ATTENTION_MAPS_MAX_DIM
         if not (0 < self.Dk <= big and 0 < self.Dv <= big):
             raise ValueError(f"{prefix}: head sizes {self.Dk} and {self.Dv} are outside 1..{big}")
+        self.qk_norm_weight, self.value_norm, self.head_mix, self.gate = bool(qk_norm_weight), bool(value_norm), head_mix, gate
+        if gate is not None and head_mix is None:
+            raise ValueError(f"{prefix}: the output gate is applied by the kernel that mixes the heads (head_mix)")
+        if head_mix is not None:
+            if self.M != 1 or sink or self.values_are_keys:
+                raise ValueError(f"{prefix}: mixed heads need one map, no sink and values of their own")
+            if self.G * self.Dv > ops.talk_max_row():
+                raise ValueError(f"{prefix}: {self.G} value heads of {self.Dv} are more than {ops.talk_max_row()} numbers per token")
         self.window = int(window) if window else None
         self.scale, self.eps = float(scale), float(eps)
         self.position, self.qk_norm, self.has_sink = position, bool(qk_norm), bool(sink)
@@ -66,10 +85,14 @@ class MapsAttention(Mixer):
         if not self.values_are_keys:
             sources.append((f"{prefix}.{v}", self.G * self.Dv))
         self.offsets = (0, n_q, n_q if self.values_are_keys else n_q + n_k)
+        self.gate_offset = None
+        if gate is not None:
+            self.gate_offset = sum(r for _, r in sources)
+            sources.append((f"{prefix}.{gate}", self.H * self.Dv))
         self.qkv = Linear(opts, width, sources, bias=bias, weight_suffix=weight_suffix, bias_suffix=bias_suffix)
         self.out = Linear(opts, self.H * self.Dv, [(f"{prefix}.{o}", width)], weight_suffix=weight_suffix,
                           out_dtype=out_dtype)
-        self.q_weight = self.k_weight = self.sink = None
+        self.q_weight = self.k_weight = self.sink = self.talk = None
         self.coef = 0.0
 
     def own_param_specs(self):
@@ -77,9 +100,11 @@ class MapsAttention(Mixer):
         specs = []
         if self.difference is not None:
             specs += [ParamSpec(f"{p}.{n}", (self.Dk,), "vector", "normal") for n in ("lq1", "lk1", "lq2", "lk2")]
-        if self.qk_norm:
+        if self.qk_norm and self.qk_norm_weight:
             specs += [ParamSpec(f"{p}.{q}.norm", (self.Dk,), "vector", "one_plus_normal"),
                       ParamSpec(f"{p}.{k}.norm", (self.Dk,), "vector", "one_plus_normal")]
+        if self.head_mix is not None:
+            specs.append(ParamSpec(f"{p}.{self.head_mix}", (self.H, self.H), "vector", "normal"))
         if self.has_sink:
             specs.append(ParamSpec(f"{p}.sink", (self.H,), "vector", "normal"))
         return specs
@@ -91,12 +116,29 @@ class MapsAttention(Mixer):
             lam = (math.exp(float((d["lq1"] * d["lk1"]).sum())) - math.exp(float((d["lq2"] * d["lk2"]).sum()))
                    + self.difference)
             self.coef = -lam
-        if self.qk_norm:
+        if self.qk_norm and self.qk_norm_weight:
             self.q_weight, self.k_weight = got[f"{self.names[0]}.norm"], got[f"{self.names[1]}.norm"]
+        elif self.qk_norm:
+            self.q_weight = self.k_weight = torch.ones(self.Dk, dtype=torch.float32, device=self.opts.device)
+        if self.head_mix is not None:
+            self.talk = got[self.head_mix].contiguous()
         if self.has_sink:
             self.sink = got["sink"]
 
+    def load(self, fetch):
+        super().load(fetch)
+        if self.head_mix is not None:
+            # query vector x = j * G + c is head c * (H/G) + j: neighbours read different key heads
+            n_q, per = self.H * self.Dk, self.H // self.G
+            w = self.qkv.weight
+            w[:n_q] = w[:n_q].reshape(self.G, per, self.Dk, -1).transpose(0, 1).reshape(n_q, -1).clone()
+            if self.qkv.bias is not None:
+                b = self.qkv.bias
+                b[:n_q] = b[:n_q].reshape(self.G, per, self.Dk).transpose(0, 1).reshape(n_q).clone()
+
     def cache_spec(self):
+        if self.head_mix is not None:       # a token's value heads side by side in one row
+            return KVSpec(self.G, self.Dk, self.window, value_heads=1, value_dim=self.G * self.Dv)
         return KVSpec(self.G * self.M, self.Dk, self.window, value_heads=self.G, value_dim=self.Dv)
 
     def _on_tensor_cores(self, buf) -> bool:
@@ -113,8 +155,15 @@ class MapsAttention(Mixer):
         rot = self.position.rotation() if self.position is not None else None
         ops.attention_prepare(buf, self.offsets, self.H, self.G, self.M, self.Dk, self.Dv, cache, ctx,
                               q_weight=self.q_weight, k_weight=self.k_weight, eps=self.eps, rot=rot,
-                              write_cache=write_cache, bias=self.qkv.bias if later else None)
+                              write_cache=write_cache, bias=self.qkv.bias if later else None,
+                              v_norm=self.value_norm, v_side_by_side=self.head_mix is not None)
         att = torch.empty((buf.shape[0], self.H * self.Dv), dtype=buf.dtype, device=buf.device)
+        if self.head_mix is not None:
+            gate_rows = buf.reshape(-1)[self.gate_offset:] if self.gate_offset is not None else None
+            ops.attention_talk(buf, buf.shape[-1], att, cache, ctx, self.H, self.G, self.Dk, self.Dv, self.scale,
+                               self.talk, gate_rows=gate_rows, gate_stride=buf.shape[-1], window=self.window or 0)
+            return self.out.forward(att, n_rows=T, start_early=False, then=then)
+
         unit = self.difference is not None
         attend = ops.attention_maps_mma if self._on_tensor_cores(buf) else ops.attention_maps
         attend(buf, buf.shape[-1], att, cache, ctx, self.H, self.G, self.M, self.Dk, self.Dv, self.scale,
