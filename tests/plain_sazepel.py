@@ -99,8 +99,12 @@ def route(h, w, router):
     return chosen, e / e.sum(axis=1, keepdims=True), z
 
 
-def experts(h, w, mlp):
-    chosen, wts, _ = route(h, w, mlp["router"])
+def experts(h, w, mlp, margins=None):
+    chosen, wts, z = route(h, w, mlp["router"])
+    if margins is not None:      # per token: how far the last chosen logit lies above the first one left out
+        zs = -np.sort(-z, axis=1)
+        top = mlp["router"]["top"]
+        margins.append(zs[:, top - 1] - zs[:, top] if top < z.shape[1] else np.full(z.shape[0], np.inf))
     out = np.zeros((h.shape[0], w["e0.down"].shape[0]))
     for t in range(h.shape[0]):
         for j, e in enumerate(chosen[t]):
@@ -113,8 +117,9 @@ def _sub(weights, prefix):
     return {k[len(prefix):]: v for k, v in weights.items() if k.startswith(prefix)}
 
 
-def forward(config, weights, tokens, trace=None):
-    """Logits [T, vocab] of the whole sequence `tokens`.  `trace`: a list that gets the stream after every layer."""
+def forward(config, weights, tokens, trace=None, margins=None):
+    """Logits [T, vocab] of the whole sequence `tokens`.  `trace`: a list that gets the stream after every layer;
+    `margins`: a list that gets, for every router, each token's gap between the last chosen logit and the next."""
     W = {k: np.asarray(v, np.float64) for k, v in weights.items()}
     eps = float(config["norm"]["eps"])
     x = unit(W["embed"][np.asarray(tokens)], eps) * W["embed.norm"]
@@ -131,7 +136,7 @@ def forward(config, weights, tokens, trace=None):
         x = x + unit(y, eps) * W[p + "norm1b"]
         if layer.get("mlp") is not None:
             h = unit(x, eps) * W[p + "norm2"]
-            x = x + unit(experts(h, _sub(W, p + "mlp."), layer["mlp"]), eps) * W[p + "norm2b"]
+            x = x + unit(experts(h, _sub(W, p + "mlp."), layer["mlp"], margins), eps) * W[p + "norm2b"]
         if trace is not None:
             trace.append(x.copy())
     return (unit(x, eps) * W["final.norm"]) @ W["head"].T * float(config["logit_scale"])
