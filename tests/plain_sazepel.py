@@ -43,8 +43,10 @@ def turn_halves(x, positions, rot):
     return out
 
 
-def retention(h, w, mx, eps, positions=None, state=None):
-    """Linear attention with a constant decay per head.  h [T, E]; returns ([T, E], final state [H, D, V])."""
+def retention(h, w, mx, eps, positions=None, state=None, cosines=None):
+    """Linear attention with a constant decay per head.  h [T, E]; returns ([T, E], final state [H, D, V]).
+    `cosines`: a list that gets, per head, |cos| of the angle between the first token's q and k: from an empty state
+    that token's output is (q . k) v, so that after the head norm only the SIGN of q . k is left."""
     T = h.shape[0]
     H, D, V = mx["heads"], mx["dim"], mx["vdim"]
     positions = np.arange(T) if positions is None else positions
@@ -52,6 +54,8 @@ def retention(h, w, mx, eps, positions=None, state=None):
     k = turn_halves((h @ w["k"].T).reshape(T, H, D), positions, mx["rot"]) * D ** -0.5
     v = (h @ w["v"].T).reshape(T, H, V)
     S = np.zeros((H, D, V)) if state is None else np.array(state, np.float64)
+    if cosines is not None:
+        cosines.append(np.abs((q[0] * k[0]).sum(-1)) / (np.linalg.norm(q[0], axis=-1) * np.linalg.norm(k[0], axis=-1) + 1e-300))
     o = np.zeros((T, H, V))
     for t in range(T):
         for a in range(H):
@@ -83,9 +87,9 @@ def talking_attention(h, w, mx, eps):
     return o @ w["o"].T
 
 
-def side_by_side(h, w, mx, eps, positions=None):
+def side_by_side(h, w, mx, eps, positions=None, cosines=None):
     left = talking_attention(h, _sub(w, "left."), mx["left"], eps)
-    right, _ = retention(h, _sub(w, "right."), mx["right"], eps, positions)
+    right, _ = retention(h, _sub(w, "right."), mx["right"], eps, positions, cosines=cosines)
     return 0.5 * (unit(left, eps) * w["left.out"] + unit(right, eps) * w["right.out"])
 
 
@@ -117,9 +121,10 @@ def _sub(weights, prefix):
     return {k[len(prefix):]: v for k, v in weights.items() if k.startswith(prefix)}
 
 
-def forward(config, weights, tokens, trace=None, margins=None):
+def forward(config, weights, tokens, trace=None, margins=None, cosines=None):
     """Logits [T, vocab] of the whole sequence `tokens`.  `trace`: a list that gets the stream after every layer;
-    `margins`: a list that gets, for every router, each token's gap between the last chosen logit and the next."""
+    `margins`: a list that gets, for every router, each token's gap between the last chosen logit and the next;
+    `cosines`: a list that gets, for every retention, what `retention` says of the first token."""
     W = {k: np.asarray(v, np.float64) for k, v in weights.items()}
     eps = float(config["norm"]["eps"])
     x = unit(W["embed"][np.asarray(tokens)], eps) * W["embed.norm"]
@@ -128,9 +133,9 @@ def forward(config, weights, tokens, trace=None, margins=None):
         h = unit(x, eps) * W[p + "norm1"]
         mix = _sub(W, p + "mix.")
         if layer["type"] == "retention":
-            y, _ = retention(h, mix, layer["mixer"], eps)
+            y, _ = retention(h, mix, layer["mixer"], eps, cosines=cosines)
         elif layer["type"] == "parallel":
-            y = side_by_side(h, mix, layer["mixer"], eps)
+            y = side_by_side(h, mix, layer["mixer"], eps, cosines=cosines)
         else:
             raise ValueError(layer["type"])
         x = x + unit(y, eps) * W[p + "norm1b"]

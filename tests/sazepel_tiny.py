@@ -6,7 +6,8 @@ over part of a vector, over all of it and over none; decays of exactly 1 and wel
 heads, one for all heads, and groups in between; routers that choose 1 of 3, 2 of 4 and all 5 of 5 experts; expert
 widths that are no multiples of 8; layers without a feed-forward; head sizes that take the tensor-core kernels in
 bfloat16 (16, 32) and ones that do not (20, 24); a logit factor away from 1.  `TINY_R` has no routers, so that a
-bfloat16 run can be compared at every position.
+bfloat16 run can be compared at every position; `make_weights(..., decided=True)` makes routers whose biases decide the
+choice (the same experts for every token, weights that still vary), for the same reason.
 
 `make_weights` draws values that a bfloat16 holds exactly, so that the plain implementation, the 32-bit engine and
 the bfloat16 engine read the same numbers.  Scales are chosen so that faults show: the layer norms' single numbers
@@ -67,15 +68,25 @@ TINY_R = {
     ],
 }
 
-CONFIGS = {"p": TINY_P, "q": TINY_Q, "r": TINY_R}
+TINY_S = {
+    "architecture": "Sazepel", "vocab": 89, "width": 32, "norm": {"eps": 1e-6}, "logit_scale": 0.5,
+    "layers": [
+        {"type": "retention", "mixer": _ret(2, 16, 16, (0.9375, 0.99), 1e4, 8), "mlp": _moe(24, 4, 2)},
+        {"type": "parallel", "mixer": {"left": _att(4, 2, 16, 32, 0.3), "right": _ret(2, 8, 8, (0.8, 1.0), 100.0, 8)},
+         "mlp": _moe(16, 5, 3)},
+    ],
+}
+
+CONFIGS = {"p": TINY_P, "q": TINY_Q, "r": TINY_R, "s": TINY_S}
 
 
 def bf16_exact(x):
     """Rounds float32 values to the nearest bfloat16 (ties to even), returned as float32."""
-    x = np.ascontiguousarray(x, dtype=np.float32)
+    shape = np.shape(x)
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
     bits = x.view(np.uint32).astype(np.uint64)
     bits = (bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000
-    return bits.astype(np.uint32).view(np.float32).reshape(x.shape)
+    return bits.astype(np.uint32).view(np.float32).reshape(shape)
 
 
 def _retention_shapes(p, mx, E):
@@ -108,7 +119,7 @@ def tensor_shapes(config) -> dict:
     return out
 
 
-def make_weights(config, seed: int, std: float = 0.1) -> dict:
+def make_weights(config, seed: int, std: float = 0.1, decided: bool = False) -> dict:
     rng = np.random.default_rng(seed)
     out = {}
     for name, shape in tensor_shapes(config).items():
@@ -120,14 +131,33 @@ def make_weights(config, seed: int, std: float = 0.1) -> dict:
         elif last == "talk":
             x = np.eye(shape[0]) * 0.8 + rng.normal(0.0, 0.5, shape)
         elif last == "b":
-            x = rng.normal(0.0, 1.0, shape)
+            x = rng.permutation(shape[0]) * 4.0 if decided else rng.normal(0.0, 1.0, shape)
         elif last == "router":
-            x = rng.normal(0.0, 0.5, shape)
+            x = rng.normal(0.0, 0.05 if decided else 0.5, shape)
         elif name == "embed":
             x = rng.normal(0.0, 1.0, shape)
         else:
             x = rng.normal(0.0, std * (48.0 / shape[-1]) ** 0.5 * 1.5, shape)
+            if last == "k" and ".left." not in name:
+                # a retention's k leans towards its q, so that q . k of one token is seldom near zero (see
+                # `sure_first_tokens`); tensor_shapes lists q before k
+                x = 0.6 * out[name[:-1] + "q"] + 0.8 * x
         out[name] = bf16_exact(np.asarray(x, np.float32))
+    return out
+
+
+def sure_first_tokens(config, weights, floor: float = 0.04) -> list:
+    """The tokens that can open a sequence in a test.  From an empty state a retention head's first output is
+    (q . k) v, of which the head norm keeps the sign of q . k alone: a token whose q and k are nearly at right angles
+    in some head of some layer gets one sign or the other by rounding (no fault, and not small).  These are the
+    tokens for which |cos(q, k)| >= floor in every head, by the plain implementation."""
+    import plain_sazepel
+    out = []
+    for t in range(config["vocab"]):
+        cosines = []
+        plain_sazepel.forward(config, weights, [t], cosines=cosines)
+        if all((c >= floor).all() for c in cosines):
+            out.append(t)
     return out
 
 
