@@ -602,31 +602,246 @@ talk_attend_kernel(TalkArgs a) {
 }
 
 // out[t, h, d] = gate * sum_g T[h, g] A[t, x(g), c(h)*Dv + d], x(g) = (g % R) * G + g / R, c(h) = h / R, R = H / G;
-// gate = sigmoid(gate_rows[t*gate_stride + h*Dv + d]) or 1.  One warp per (token, head).
+// gate = sigmoid(gate_rows[t*gate_stride + h*Dv + d]) or 1.  A thread per column c*Dv + d of a token's rows of A: it
+// reads that column of all H rows once (neighbouring threads neighbouring addresses) and writes the R heads of
+// group c, four at a time.  The mixing matrix waits in shared memory (`talk_smem`: it fits).  With `ml`: A holds
+// `parts` partial rows per (token, x), [T, parts, H, W] sums of exp(score - m) * v with their (m, l) in
+// ml [T, parts, H, 2] (m in units of log2; a part without keys has l = 0): they are merged on the way.
 template <typename T>
 __global__ void __launch_bounds__(128)
-talk_combine_kernel(const float* __restrict__ A, const float* __restrict__ talk, const T* __restrict__ gate_rows,
-                    int gate_stride, T* __restrict__ out, const int* __restrict__ tok_seq, int n_tokens, int H, int G,
-                    int Dv) {
+talk_combine_kernel(const float* __restrict__ A, const float* __restrict__ ml, int parts,
+                    const float* __restrict__ talk, const T* __restrict__ gate_rows, int gate_stride,
+                    T* __restrict__ out, const int* __restrict__ tok_seq, int n_tokens, int H, int G, int Dv,
+                    int talk_smem) {
+  extern __shared__ float tc_smem[];       // talk [H*H] (if talk_smem), then the parts' weights [parts*H] (if ml is given)
   pdl_wait();
   pdl_trigger();
-  const int lane = threadIdx.x & 31;
-  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (w >= (long long)n_tokens * H) return;
-  const int t = (int)(w / H), h = (int)(w - (long long)t * H);
-  T* o = out + (size_t)w * Dv;
-  if (tok_seq[t] < 0) {
-    for (int d = lane; d < Dv; d += 32) o[d] = from_f32<T>(0.f);
+  const int t = blockIdx.x;
+  const int W = G * Dv, R = H / G;
+  const int col = blockIdx.y * blockDim.x + threadIdx.x;
+  const bool live = tok_seq[t] >= 0;
+  float* wts = tc_smem + (talk_smem ? H * H : 0);
+  if (live) {
+    if (talk_smem)
+      for (int i = threadIdx.x; i < H * H; i += blockDim.x) tc_smem[i] = talk[i];
+    if (ml != nullptr) {
+      // weight of part p for row x: exp2(m_p - m) / sum over parts of l_p exp2(m_p - m)
+      for (int x = threadIdx.x; x < H; x += blockDim.x) {
+        const float* mlx = ml + ((size_t)t * parts * H + x) * 2;
+        float m = -INFINITY;
+        for (int p = 0; p < parts; ++p)
+          if (mlx[(size_t)p * H * 2 + 1] > 0.f) m = fmaxf(m, mlx[(size_t)p * H * 2]);
+        float l = 0.f;
+        for (int p = 0; p < parts; ++p) {
+          const float lp = mlx[(size_t)p * H * 2 + 1];
+          if (lp > 0.f) l += lp * exp2f(mlx[(size_t)p * H * 2] - m);
+        }
+        for (int p = 0; p < parts; ++p) {
+          const float lp = mlx[(size_t)p * H * 2 + 1];
+          wts[p * H + x] = (lp > 0.f && l > 0.f) ? exp2f(mlx[(size_t)p * H * 2] - m) / l : 0.f;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (col >= W) return;
+  const int c = col / Dv, d = col - c * Dv;
+  if (!live) {
+    for (int j = 0; j < R; ++j) out[((size_t)t * H + c * R + j) * Dv + d] = from_f32<T>(0.f);
     return;
   }
-  const int R = H / G, c = h / R, W = G * Dv;
-  const float* At = A + (size_t)t * H * W + (size_t)c * Dv;
-  const float* Th = talk + (size_t)h * H;
-  for (int d = lane; d < Dv; d += 32) {
-    float sum = 0.f;
-    for (int g = 0; g < H; ++g) sum = fmaf(Th[g], At[(size_t)((g % R) * G + g / R) * W + d], sum);
-    if (gate_rows != nullptr) sum *= 1.0f / (1.0f + expf(-to_f32(gate_rows[(size_t)t * gate_stride + h * Dv + d])));
-    o[d] = from_f32<T>(sum);
+  const float* tk = talk_smem ? tc_smem : talk;
+  const float* At = A + (size_t)t * parts * H * W + col;
+  for (int j0 = 0; j0 < R; j0 += 4) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int x = 0; x < H; ++x) {
+      const int g = (x % G) * R + x / G;
+      float a;
+      if (ml != nullptr) {
+        a = 0.f;
+        for (int p = 0; p < parts; ++p) {
+          const float wp = wts[p * H + x];
+          if (wp != 0.f) a = fmaf(wp, At[((size_t)p * H + x) * W], a);
+        }
+      } else {
+        a = At[(size_t)x * W];
+      }
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj)
+        if (j0 + jj < R) acc[jj] = fmaf(tk[(size_t)(c * R + j0 + jj) * H + g], a, acc[jj]);
+    }
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      if (j0 + jj >= R) break;
+      const int h = c * R + j0 + jj;
+      float sum = acc[jj];
+      if (gate_rows != nullptr) sum *= 1.0f / (1.0f + expf(-to_f32(gate_rows[(size_t)t * gate_stride + h * Dv + d])));
+      out[((size_t)t * H + h) * Dv + d] = from_f32<T>(sum);
+    }
+  }
+}
+
+// One token per sequence: the keys of a token are cut into `parts` runs of `pages_per_part` pages, and a CTA takes
+// (token, key head kh, part, up to 4 of the R query vectors that read kh, up to 512 of the G*Dv value columns), so that
+// a step of few tokens fills the device.  It leaves sums of exp2(score - m) * v in Ap [T, parts, H, W] and (m, l) in
+// ml [T, parts, H, 2]; `talk_combine` merges the parts.  Scores are float32 sums over the key's dims in order; a
+// thread owns 4 neighbouring value columns.  The geometry depends on the block table's width alone, the lengths are
+// read from device memory: a captured step stays valid while its sequences grow.
+#define TD_KEYS 64
+#define TD_RC 4
+#define TD_COLS 512
+template <typename T>
+__global__ void __launch_bounds__(128)
+talk_decode_kernel(TalkArgs a, float* __restrict__ ml, int parts, int pages_per_part, int r_chunks, int col_blocks) {
+  extern __shared__ __align__(16) unsigned char td_raw[];
+  pdl_wait();
+  pdl_trigger();
+  const int Dk = a.Dk, W = a.G * a.Dv, R = a.H / a.G, H = a.H;
+  float* qs = reinterpret_cast<float*>(td_raw);             // [TD_RC][Dk]
+  float* ps = qs + TD_RC * Dk;                               // [TD_RC][TD_KEYS]
+  float* corr = ps + TD_RC * TD_KEYS;                        // [TD_RC]
+  T* ks = reinterpret_cast<T*>(corr + TD_RC);                // [TD_KEYS][Dk + pad]
+  const int kpitch = Dk + (16 / (int)sizeof(T));
+  int idx = blockIdx.x;
+  const int cb = idx % col_blocks; idx /= col_blocks;
+  const int rc = idx % r_chunks; idx /= r_chunks;
+  const int p = idx % parts; idx /= parts;
+  const int kh = idx % a.G;
+  const int t = idx / a.G;
+  const int b = a.tok_seq[t];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int j0 = rc * TD_RC, nr = min(TD_RC, R - j0);       // query vectors x = (j0 + r) * G + kh, r < nr
+  const int col = cb * TD_COLS + tid * 4;
+  float* mlo = ml + ((size_t)t * parts + p) * H * 2;
+  if (b < 0) {
+    if (cb == 0 && tid < nr) { mlo[((j0 + tid) * a.G + kh) * 2] = -INFINITY; mlo[((j0 + tid) * a.G + kh) * 2 + 1] = 0.f; }
+    return;
+  }
+  const int pos = a.tok_pos[t];
+  const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+  const int page0 = lo / a.page_size + p * pages_per_part;
+  const int page1 = min(page0 + pages_per_part, pos / a.page_size + 1);
+  if (page0 >= page1) {
+    if (cb == 0 && tid < nr) { mlo[((j0 + tid) * a.G + kh) * 2] = -INFINITY; mlo[((j0 + tid) * a.G + kh) * 2 + 1] = 0.f; }
+    return;
+  }
+  const T* qrow = reinterpret_cast<const T*>(a.q) + (size_t)t * a.q_stride;
+  for (int i = tid; i < nr * Dk; i += 128) {
+    const int r = i / Dk, d = i - r * Dk;
+    qs[i] = to_f32(qrow[(size_t)((j0 + r) * a.G + kh) * Dk + d]) * a.scale * 1.4426950408889634f;
+  }
+  const int* bt = a.block_table + (size_t)b * a.table_width;
+  const T* kp = reinterpret_cast<const T*>(a.k_pages);
+  const T* vp = reinterpret_cast<const T*>(a.v_pages);
+  float acc[TD_RC][4];
+#pragma unroll
+  for (int r = 0; r < TD_RC; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;      // of row r = warp (a warp per query vector), kept by every lane
+  const bool own_col = col < W && col < (cb + 1) * TD_COLS;
+  for (int pg = page0; pg < page1; ++pg) {
+    const int page = bt[pg];
+    const int key0 = pg * a.page_size;
+    const int n_keys = min(a.page_size, pos - key0 + 1);
+    __syncthreads();                          // the tile and the weights of the page before are done with
+    {
+      // the page's keys of head kh, 16 bytes at a time
+      const T* src = kp + ((size_t)page * a.G + kh) * a.page_size * Dk;
+      constexpr int PER = 16 / (int)sizeof(T);
+      const int cpr = Dk / PER;
+      for (int c = tid; c < n_keys * cpr; c += 128) {
+        const int k = c / cpr, cc = c - k * cpr;
+        *reinterpret_cast<uint4*>(ks + k * kpitch + cc * PER) = *reinterpret_cast<const uint4*>(src + (size_t)k * Dk + cc * PER);
+      }
+    }
+    __syncthreads();
+    // scores: thread (key, half) takes the rows r = half and half + 2, the key's numbers 16 bytes at a time
+    {
+      const int k = tid & 63, half = tid >> 6;
+      constexpr int PER = 16 / (int)sizeof(T);
+      float s0 = 0.f, s1 = 0.f;
+      const bool seen = k < n_keys && key0 + k >= lo;
+      if (seen && half < nr) {
+        const T* kr = ks + k * kpitch;
+        const float* q0 = qs + half * Dk;
+        const float* q1 = qs + (half + 2 < nr ? half + 2 : half) * Dk;
+        for (int d = 0; d < Dk; d += PER) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(kr + d);
+          float kv[PER];
+          if (sizeof(T) == 2) {
+            kv[0] = __uint_as_float(raw.x << 16); kv[1] = __uint_as_float(raw.x & 0xffff0000u);
+            kv[2] = __uint_as_float(raw.y << 16); kv[3] = __uint_as_float(raw.y & 0xffff0000u);
+            if (PER > 4) {
+              kv[PER - 4] = __uint_as_float(raw.z << 16); kv[PER - 3] = __uint_as_float(raw.z & 0xffff0000u);
+              kv[PER - 2] = __uint_as_float(raw.w << 16); kv[PER - 1] = __uint_as_float(raw.w & 0xffff0000u);
+            }
+          } else {
+            kv[0] = __uint_as_float(raw.x); kv[1] = __uint_as_float(raw.y);
+            kv[2] = __uint_as_float(raw.z); kv[3] = __uint_as_float(raw.w);
+          }
+#pragma unroll
+          for (int i = 0; i < PER; ++i) {
+            s0 = fmaf(q0[d + i], kv[i], s0);
+            s1 = fmaf(q1[d + i], kv[i], s1);
+          }
+        }
+      }
+      if (half < nr) ps[half * TD_KEYS + k] = seen ? s0 : -INFINITY;
+      if (half + 2 < nr) ps[(half + 2) * TD_KEYS + k] = seen ? s1 : -INFINITY;
+    }
+    __syncthreads();
+    // a warp per row: the running maximum and sum, the weights in place of the scores
+    if (warp < nr) {
+      const float s0 = ps[warp * TD_KEYS + lane], s1 = ps[warp * TD_KEYS + lane + 32];
+      const float m_new = fmaxf(m_run, warp_max(fmaxf(s0, s1)));
+      const float c0 = (m_new == -INFINITY) ? 1.f : exp2f(m_run - m_new);
+      const float p0 = (s0 == -INFINITY) ? 0.f : exp2f(s0 - m_new), p1 = (s1 == -INFINITY) ? 0.f : exp2f(s1 - m_new);
+      ps[warp * TD_KEYS + lane] = p0;
+      ps[warp * TD_KEYS + lane + 32] = p1;
+      l_run = l_run * c0 + warp_sum(p0 + p1);
+      m_run = m_new;
+      if (lane == 0) corr[warp] = c0;
+    }
+    __syncthreads();
+    if (own_col) {
+#pragma unroll
+      for (int r = 0; r < TD_RC; ++r) {
+        const float c0 = r < nr ? corr[r] : 1.f;
+        acc[r][0] *= c0; acc[r][1] *= c0; acc[r][2] *= c0; acc[r][3] *= c0;
+      }
+      const T* vrow = vp + ((size_t)page * a.page_size) * W + col;
+#pragma unroll 4
+      for (int k = 0; k < n_keys; ++k) {
+        float v0, v1, v2, v3;
+        if (sizeof(T) == 2) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(vrow + (size_t)k * W);
+          v0 = __uint_as_float(raw.x << 16); v1 = __uint_as_float(raw.x & 0xffff0000u);
+          v2 = __uint_as_float(raw.y << 16); v3 = __uint_as_float(raw.y & 0xffff0000u);
+        } else {
+          const float4 raw = *reinterpret_cast<const float4*>(vrow + (size_t)k * W);
+          v0 = raw.x; v1 = raw.y; v2 = raw.z; v3 = raw.w;
+        }
+#pragma unroll
+        for (int r = 0; r < TD_RC; ++r) {
+          const float pk = ps[r * TD_KEYS + k];      // rows past nr hold what was there: their sums are not stored
+          acc[r][0] = fmaf(pk, v0, acc[r][0]);
+          acc[r][1] = fmaf(pk, v1, acc[r][1]);
+          acc[r][2] = fmaf(pk, v2, acc[r][2]);
+          acc[r][3] = fmaf(pk, v3, acc[r][3]);
+        }
+      }
+    }
+  }
+  if (cb == 0 && warp < nr && lane == 0) {
+    mlo[((j0 + warp) * a.G + kh) * 2] = m_run;
+    mlo[((j0 + warp) * a.G + kh) * 2 + 1] = l_run;
+  }
+  if (own_col) {
+#pragma unroll
+    for (int r = 0; r < TD_RC; ++r)
+      if (r < nr) {
+        float* o = a.A + (((size_t)t * parts + p) * H + (j0 + r) * a.G + kh) * W + col;
+        *reinterpret_cast<float4*>(o) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+      }
   }
 }
 
@@ -668,19 +883,67 @@ AB_API int ab_talk_attend(const void* q, int q_stride, float* A, int dtype, cons
   return AB_BAD_ARG;
 }
 
-AB_API int ab_talk_combine(const float* A, const float* talk, const void* gate_rows, int gate_stride, void* out, int dtype,
-                           const int* tok_seq, int n_tokens, int H, int G, int Dv, cudaStream_t stream) {
+// `ml` given: A [T, parts, H, G*Dv] and ml [T, parts, H, 2] hold partial sums over parts of the keys (see the kernel);
+// without it parts is 1 and A holds the finished rows.
+AB_API int ab_talk_combine_parts(const float* A, const float* ml, int parts, const float* talk, const void* gate_rows,
+                                 int gate_stride, void* out, int dtype, const int* tok_seq, int n_tokens, int H, int G,
+                                 int Dv, cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
-  if (H <= 0 || G <= 0 || H % G || Dv <= 0) return AB_BAD_ARG;
-  const long long warps = (long long)n_tokens * H;
-  const unsigned blocks = (unsigned)((warps + 3) / 4);
+  if (H <= 0 || G <= 0 || H % G || Dv <= 0 || parts < 1 || (parts > 1 && !ml) || !tok_seq) return AB_BAD_ARG;
+  const int W = G * Dv;
+  size_t smem = ml ? (size_t)parts * H * sizeof(float) : 0;
+  const int talk_smem = (size_t)H * H * sizeof(float) + smem <= 40 * 1024 ? 1 : 0;
+  if (talk_smem) smem += (size_t)H * H * sizeof(float);
+  if (smem > 48 * 1024) return AB_BAD_ARG;
+  dim3 grid((unsigned)n_tokens, (unsigned)((W + 127) / 128));
   if (dtype == AB_F32)
-    ab_launch(talk_combine_kernel<float>, dim3(blocks), dim3(128), 0, stream, A, talk, (const float*)gate_rows, gate_stride,
-              (float*)out, tok_seq, n_tokens, H, G, Dv);
+    ab_launch(talk_combine_kernel<float>, grid, dim3(128), smem, stream, A, ml, parts, talk, (const float*)gate_rows,
+              gate_stride, (float*)out, tok_seq, n_tokens, H, G, Dv, talk_smem);
   else if (dtype == AB_BF16)
-    ab_launch(talk_combine_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, A, talk, (const bf16*)gate_rows, gate_stride,
-              (bf16*)out, tok_seq, n_tokens, H, G, Dv);
+    ab_launch(talk_combine_kernel<bf16>, grid, dim3(128), smem, stream, A, ml, parts, talk, (const bf16*)gate_rows,
+              gate_stride, (bf16*)out, tok_seq, n_tokens, H, G, Dv, talk_smem);
   else
     return AB_BAD_ARG;
+  return ab_launch_status();
+}
+
+AB_API int ab_talk_combine(const float* A, const float* talk, const void* gate_rows, int gate_stride, void* out, int dtype,
+                           const int* tok_seq, int n_tokens, int H, int G, int Dv, cudaStream_t stream) {
+  return ab_talk_combine_parts(A, nullptr, 1, talk, gate_rows, gate_stride, out, dtype, tok_seq, n_tokens, H, G, Dv, stream);
+}
+
+// The decode form: one token per sequence, the keys in `parts` runs of `pages_per_part` pages (see the kernel).
+// Ap float [T, parts, H, G*Dv], ml float [T, parts, H, 2].  Sizes: Dk in 16-byte pieces, G*Dv a multiple of 4.
+AB_API int ab_talk_decode(const void* q, int q_stride, float* Ap, float* ml, int parts, int pages_per_part, int dtype,
+                          const void* k_pages, const void* v_pages, const int* block_table, int table_width,
+                          const int* tok_pos, const int* tok_seq, int n_tokens, int H, int G, int Dk, int Dv,
+                          int page_size, float scale, int window, cudaStream_t stream) {
+  if (n_tokens <= 0) return AB_OK;
+  if (Dk <= 0 || Dv <= 0 || H <= 0 || G <= 0 || H % G || page_size != TD_KEYS || parts < 1 || pages_per_part < 1)
+    return AB_BAD_ARG;
+  const int W = G * Dv, R = H / G;
+  const int per = dtype == AB_BF16 ? 8 : 4;
+  if (Dk % per || W % 4) return AB_BAD_ARG;
+  const int r_chunks = (R + TD_RC - 1) / TD_RC, col_blocks = (W + TD_COLS - 1) / TD_COLS;
+  const long long blocks = (long long)n_tokens * G * parts * r_chunks * col_blocks;
+  if (blocks > 0x7fffffffLL) return AB_BAD_ARG;
+  TalkArgs a{q, q_stride, Ap, k_pages, v_pages, block_table, table_width, tok_pos, tok_seq, n_tokens, H, G, Dk, Dv,
+             page_size, scale, window};
+  const size_t esz = dtype == AB_BF16 ? 2 : 4;
+  const size_t smem = (size_t)(TD_RC * Dk + TD_RC * TD_KEYS + TD_RC) * sizeof(float) + (size_t)TD_KEYS * (Dk + 16 / esz) * esz;
+#define AB_GO(T)                                                                                                    \
+  {                                                                                                                 \
+    if (smem > 48 * 1024) {                                                                                         \
+      cudaError_t e = cudaFuncSetAttribute(talk_decode_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                           (int)smem);                                                              \
+      if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                            \
+    }                                                                                                               \
+    ab_launch(talk_decode_kernel<T>, dim3((unsigned)blocks), dim3(128), smem, stream, a, ml, parts, pages_per_part,  \
+              r_chunks, col_blocks);                                                                                \
+  }
+  if (dtype == AB_BF16) AB_GO(bf16)
+  else if (dtype == AB_F32) AB_GO(float)
+  else return AB_BAD_ARG;
+#undef AB_GO
   return ab_launch_status();
 }

@@ -149,17 +149,23 @@ __device__ __forceinline__ void init_state(RowState<DMAX>& st) {
 }
 
 // copies one page tile [64][D] (contiguous in global memory) into shared memory [64][pitch]
-__device__ __forceinline__ void load_tile_async(bf16* dst, const bf16* src, int D, int pitch, int tid, int nthreads) {
+// (`src_row`: the numbers between two rows of the source; D for a tile that is contiguous, more for D columns of
+// wider rows)
+__device__ __forceinline__ void load_tile_async(bf16* dst, const bf16* src, int D, int pitch, int tid, int nthreads,
+                                                int src_row) {
   const int cpr = D >> 3;                 // 16-byte chunks per row
   if (nthreads % cpr == 0) {              // a thread keeps its column and walks down the rows
     const int cc = tid % cpr, dr = nthreads / cpr;
-    for (int r = tid / cpr; r < PAGE; r += dr) cp_async_16(dst + r * pitch + cc * 8, src + (size_t)r * D + cc * 8);
+    for (int r = tid / cpr; r < PAGE; r += dr) cp_async_16(dst + r * pitch + cc * 8, src + (size_t)r * src_row + cc * 8);
     return;
   }
   for (int c = tid; c < PAGE * cpr; c += nthreads) {
     const int r = c / cpr, cc = c - r * cpr;
-    cp_async_16(dst + r * pitch + cc * 8, src + (size_t)r * D + cc * 8);
+    cp_async_16(dst + r * pitch + cc * 8, src + (size_t)r * src_row + cc * 8);
   }
+}
+__device__ __forceinline__ void load_tile_async(bf16* dst, const bf16* src, int D, int pitch, int tid, int nthreads) {
+  load_tile_async(dst, src, D, pitch, tid, nthreads, D);
 }
 
 // A sink: a learned logit per head whose exp joins the softmax's denominator and which has no value.  `m` is
@@ -176,7 +182,9 @@ __device__ __forceinline__ float sum_with_sink(float l, float m, const float* __
 // vectors (g*G + j)*M + m, j < G: a head's maps lie side by side in a token's row).  M = 1, Dv = D is plain
 // grouped-query attention.  out: bfloat16 [T, H, Dv], or float when out_f32 is set (maps that are combined
 // afterwards).  tok_seq (or null): tiles whose first token has no sequence are skipped (padding rows of a
-// captured step of one token each).  DMAX covers both D and Dv.
+// captured step of one token each).  DMAX covers both D and Dv.  The Dv columns may be a part of wider value rows:
+// a value row has `v_row` numbers of which this launch reads columns v_col0 .. v_col0 + Dv, and an output vector
+// has v_row numbers of which it writes the same columns (v_row = Dv, v_col0 = 0: all of it).
 template <int DMAX>
 __global__ void __launch_bounds__(128)
 attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, void* __restrict__ out_any, int out_f32,
@@ -184,7 +192,8 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, void* __res
                          const int* __restrict__ block_table, int table_width, const int* __restrict__ tok_pos,
                          const int* __restrict__ cu_q, const int* __restrict__ tok_seq,
                          const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int H, int K, int M, int D,
-                         int Dv, float scale_log2, int window, int tokens_per_tile, const float* __restrict__ sink) {
+                         int Dv, float scale_log2, int window, int tokens_per_tile, const float* __restrict__ sink,
+                         int v_row, int v_col0) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int pitch = D + 8, pitch_v = Dv + 8;
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);            // [64][pitch]
@@ -235,9 +244,9 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, void* __res
 
   auto issue = [&](int kb, int stage) {
     const size_t base = ((size_t)bt[kb] * K + kh) * PAGE * D;
-    const size_t base_v = ((size_t)bt[kb] * (K / M) + grp) * PAGE * Dv;
+    const size_t base_v = ((size_t)bt[kb] * (K / M) + grp) * PAGE * v_row + v_col0;
     load_tile_async(kbuf + stage * 64 * pitch, k_pages + base, D, pitch, tid, 128);
-    load_tile_async(vbuf + stage * 64 * pitch_v, v_pages + base_v, Dv, pitch_v, tid, 128);
+    load_tile_async(vbuf + stage * 64 * pitch_v, v_pages + base_v, Dv, pitch_v, tid, 128, v_row);
     cp_async_commit();
   };
   issue(kb_begin, 0);
@@ -264,8 +273,8 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, void* __res
   if (r0 < n_rows) l0 = sum_with_sink(l0, st.m[0], sink, grp * G + r0 % G);
   if (r1 < n_rows) l1 = sum_with_sink(l1, st.m[1], sink, grp * G + r1 % G);
   const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
-  const size_t o0 = ((size_t)(q0 + r0 / G) * H + (grp * G + r0 % G) * M + map) * Dv;
-  const size_t o1 = ((size_t)(q0 + r1 / G) * H + (grp * G + r1 % G) * M + map) * Dv;
+  const size_t o0 = ((size_t)(q0 + r0 / G) * H + (grp * G + r0 % G) * M + map) * v_row + v_col0;
+  const size_t o1 = ((size_t)(q0 + r1 / G) * H + (grp * G + r1 % G) * M + map) * v_row + v_col0;
 #pragma unroll
   for (int dt = 0; dt < DMAX / 8; ++dt) {
     if (dt * 8 < Dv) {
@@ -697,14 +706,18 @@ AB_API int ab_attention_decode_round_pages(int D) { return ab_attention_decode_r
 
 // The general form (see the kernel): H query vectors, K key heads of D dims, K / M value heads of Dv dims.
 // `sink`: float [H / M] or null (see sum_with_sink); `tok_seq`: int [n_tokens] or null.
-AB_API int ab_attention_prefill_maps_bf16(const void* qkv, int q_stride, void* out, int out_f32, const void* k_pages,
-                                          const void* v_pages, const int* block_table, int table_width,
-                                          const int* tok_pos, const int* cu_q, const int* tok_seq, const int* tile_seq,
-                                          const int* tile_q0, int n_tiles, int tokens_per_tile, int H, int K, int M, int D,
-                                          int Dv, float scale, int window, const float* sink, cudaStream_t stream) {
+// `v_row`, `v_col0`: columns v_col0 .. v_col0 + Dv of value rows and output vectors of v_row numbers (both multiples
+// of 8: 16-byte pieces).
+AB_API int ab_attention_prefill_maps_cols_bf16(const void* qkv, int q_stride, void* out, int out_f32, const void* k_pages,
+                                               const void* v_pages, const int* block_table, int table_width,
+                                               const int* tok_pos, const int* cu_q, const int* tok_seq,
+                                               const int* tile_seq, const int* tile_q0, int n_tiles, int tokens_per_tile,
+                                               int H, int K, int M, int D, int Dv, float scale, int window,
+                                               const float* sink, int v_row, int v_col0, cudaStream_t stream) {
   if (n_tiles <= 0) return AB_OK;
   if (D <= 0 || D > 256 || (D % 16) || Dv <= 0 || Dv > 256 || (Dv % 16) || K <= 0 || H % K || K > 65535 || M <= 0 || K % M)
     return AB_BAD_ARG;
+  if (v_col0 < 0 || v_col0 + Dv > v_row || (v_row % 8) || (v_col0 % 8)) return AB_BAD_ARG;
   const int G = H / K;
   if (tokens_per_tile < 1 || tokens_per_tile * G > 64) return AB_BAD_ARG;
   const int pitch = D + 8, pitch_v = Dv + 8;
@@ -719,7 +732,8 @@ AB_API int ab_attention_prefill_maps_bf16(const void* qkv, int q_stride, void* o
     if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                             \
     ab_launch(attention_prefill_kernel<DM>, grid, dim3(128), smem, stream,                                         \
         (const bf16*)qkv, q_stride, out, out_f32, (const bf16*)k_pages, (const bf16*)v_pages, block_table,         \
-        table_width, tok_pos, cu_q, tok_seq, tile_seq, tile_q0, H, K, M, D, Dv, sl, window, tokens_per_tile, sink); \
+        table_width, tok_pos, cu_q, tok_seq, tile_seq, tile_q0, H, K, M, D, Dv, sl, window, tokens_per_tile, sink, \
+        v_row, v_col0);                                                                                            \
   }
   switch (dmax_of(D > Dv ? D : Dv)) {
     case 64: AB_GO(64); break;
@@ -728,6 +742,16 @@ AB_API int ab_attention_prefill_maps_bf16(const void* qkv, int q_stride, void* o
   }
 #undef AB_GO
   return ab_launch_status();
+}
+
+AB_API int ab_attention_prefill_maps_bf16(const void* qkv, int q_stride, void* out, int out_f32, const void* k_pages,
+                                          const void* v_pages, const int* block_table, int table_width,
+                                          const int* tok_pos, const int* cu_q, const int* tok_seq, const int* tile_seq,
+                                          const int* tile_q0, int n_tiles, int tokens_per_tile, int H, int K, int M, int D,
+                                          int Dv, float scale, int window, const float* sink, cudaStream_t stream) {
+  return ab_attention_prefill_maps_cols_bf16(qkv, q_stride, out, out_f32, k_pages, v_pages, block_table, table_width,
+                                             tok_pos, cu_q, tok_seq, tile_seq, tile_q0, n_tiles, tokens_per_tile, H, K, M,
+                                             D, Dv, scale, window, sink, Dv, 0, stream);
 }
 
 // `sink`: float [H] or null (see sum_with_sink).

@@ -277,12 +277,145 @@ post_norm_add_kernel(float* __restrict__ x, const TA* __restrict__ a, const TA* 
   for (int j = threadIdx.x; j < width; j += blockDim.x) o[j] = from_f32<TO>(pn_row[j] * ix * w_next[j]);
 }
 
+// Four numbers of a row per access (widths that are multiples of 4).
+template <typename T> struct Row4;
+template <> struct Row4<float> {
+  float4 v;
+  __device__ __forceinline__ void load(const float* p) { v = *reinterpret_cast<const float4*>(p); }
+  __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }
+  __device__ __forceinline__ float4 get() const { return v; }
+  __device__ __forceinline__ void set(float4 a) { v = a; }
+};
+template <> struct Row4<bf16> {
+  uint2 v;
+  __device__ __forceinline__ void load(const bf16* p) { v = *reinterpret_cast<const uint2*>(p); }
+  __device__ __forceinline__ void store(bf16* p) const { *reinterpret_cast<uint2*>(p) = v; }
+  __device__ __forceinline__ float4 get() const {
+    return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16),
+                       __uint_as_float(v.y & 0xffff0000u));
+  }
+  __device__ __forceinline__ void set(float4 a) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+  }
+};
+__device__ __forceinline__ float sq4(float4 v) { return v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+
+// The same for rows short enough that a thread keeps its share in registers (up to RV x 4 numbers per thread): the
+// sub-layer's outputs, the stream's row and every weight are asked for at once and read once.  TWO: two inputs.
+template <typename TA, typename TO, int RV, bool TWO>
+__global__ void __launch_bounds__(512)
+post_norm_add_reg_kernel(float* __restrict__ x, const TA* __restrict__ a, const TA* __restrict__ b,
+                         const float* __restrict__ wa, const float* __restrict__ wb, const float* __restrict__ w,
+                         const float* __restrict__ w_next, TO* __restrict__ out, const int* __restrict__ tok_seq,
+                         int width, float eps) {
+  __shared__ float scratch[32];
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  if (tok_seq != nullptr && tok_seq[t] < 0) {
+    if (out != nullptr)
+      for (int j = threadIdx.x; j < width; j += blockDim.x) out[(size_t)t * width + j] = from_f32<TO>(0.f);
+    return;
+  }
+  const size_t row = (size_t)t * width;
+  const float n = (float)width;
+  float4 y[RV], xv[RV], wv[RV], wn[RV], wav[RV], wbv[RV], bv[RV];
+#pragma unroll
+  for (int j = 0; j < RV; ++j) {
+    const int i = (threadIdx.x + j * blockDim.x) * 4;
+    if (i < width) {
+      Row4<TA> r;
+      r.load(a + row + i);
+      y[j] = r.get();
+      if (TWO) {
+        r.load(b + row + i);
+        bv[j] = r.get();
+        wav[j] = *reinterpret_cast<const float4*>(wa + i);
+        wbv[j] = *reinterpret_cast<const float4*>(wb + i);
+      }
+      xv[j] = *reinterpret_cast<const float4*>(x + row + i);
+      wv[j] = *reinterpret_cast<const float4*>(w + i);
+      if (out != nullptr) wn[j] = *reinterpret_cast<const float4*>(w_next + i);
+    }
+  }
+  float sa = 0.f, sb = 0.f;
+#pragma unroll
+  for (int j = 0; j < RV; ++j)
+    if ((threadIdx.x + j * blockDim.x) * 4 < width) {
+      sa += sq4(y[j]);
+      if (TWO) sb += sq4(bv[j]);
+    }
+  sa = block_sum(sa, scratch);
+  if (TWO) {
+    sb = block_sum(sb, scratch);
+    const float ia = 1.0f / sqrtf(sa / n + eps), ib = 1.0f / sqrtf(sb / n + eps);
+    sa = 0.f;
+#pragma unroll
+    for (int j = 0; j < RV; ++j)
+      if ((threadIdx.x + j * blockDim.x) * 4 < width) {
+        y[j].x = 0.5f * (y[j].x * ia * wav[j].x + bv[j].x * ib * wbv[j].x);
+        y[j].y = 0.5f * (y[j].y * ia * wav[j].y + bv[j].y * ib * wbv[j].y);
+        y[j].z = 0.5f * (y[j].z * ia * wav[j].z + bv[j].z * ib * wbv[j].z);
+        y[j].w = 0.5f * (y[j].w * ia * wav[j].w + bv[j].w * ib * wbv[j].w);
+        sa += sq4(y[j]);
+      }
+    sa = block_sum(sa, scratch);
+  }
+  const float inv = 1.0f / sqrtf(sa / n + eps);
+  float sx = 0.f;
+#pragma unroll
+  for (int j = 0; j < RV; ++j) {
+    const int i = (threadIdx.x + j * blockDim.x) * 4;
+    if (i < width) {
+      xv[j].x += y[j].x * inv * wv[j].x;
+      xv[j].y += y[j].y * inv * wv[j].y;
+      xv[j].z += y[j].z * inv * wv[j].z;
+      xv[j].w += y[j].w * inv * wv[j].w;
+      *reinterpret_cast<float4*>(x + row + i) = xv[j];
+      sx += sq4(xv[j]);
+    }
+  }
+  if (out == nullptr) return;
+  sx = block_sum(sx, scratch);
+  const float ix = 1.0f / sqrtf(sx / n + eps);
+#pragma unroll
+  for (int j = 0; j < RV; ++j) {
+    const int i = (threadIdx.x + j * blockDim.x) * 4;
+    if (i < width) {
+      Row4<TO> o;
+      o.set(make_float4(xv[j].x * ix * wn[j].x, xv[j].y * ix * wn[j].y, xv[j].z * ix * wn[j].z, xv[j].w * ix * wn[j].w));
+      o.store(out + row + i);
+    }
+  }
+}
+
 // a, b: [n_rows, width] of dtype `in_dtype` (b, wa, wb null: one input); out of dtype `out_dtype` or null.
 AB_API int ab_post_norm_add(float* x, const void* a, const void* b, int in_dtype, const float* wa, const float* wb,
                             const float* w, const float* w_next, void* out, int out_dtype, const int* tok_seq, int n_rows,
                             int width, float eps, cudaStream_t stream) {
   if (n_rows <= 0 || width <= 0) return AB_OK;
   if (!x || !a || !w || (b && (!wa || !wb)) || (out && !w_next)) return AB_BAD_ARG;
+  const bool out_f32 = out == nullptr || out_dtype == AB_F32;
+  if (!out_f32 && out_dtype != AB_BF16) return AB_BAD_ARG;
+  if (in_dtype != AB_F32 && in_dtype != AB_BF16) return AB_BAD_ARG;
+  const int vthreads = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
+  if (width % 4 == 0 && width <= vthreads * 4 * 4) {
+#define AB_REG(TA, TO)                                                                                               \
+  {                                                                                                                  \
+    if (b != nullptr)                                                                                                \
+      ab_launch(post_norm_add_reg_kernel<TA, TO, 4, true>, dim3((unsigned)n_rows), dim3(vthreads), 0, stream, x,     \
+                (const TA*)a, (const TA*)b, wa, wb, w, w_next, (TO*)out, tok_seq, width, eps);                       \
+    else                                                                                                             \
+      ab_launch(post_norm_add_reg_kernel<TA, TO, 4, false>, dim3((unsigned)n_rows), dim3(vthreads), 0, stream, x,    \
+                (const TA*)a, (const TA*)b, wa, wb, w, w_next, (TO*)out, tok_seq, width, eps);                       \
+  }
+    if (in_dtype == AB_F32) { if (out_f32) AB_REG(float, float) else AB_REG(float, bf16) }
+    else { if (out_f32) AB_REG(bf16, float) else AB_REG(bf16, bf16) }
+#undef AB_REG
+    return ab_launch_status();
+  }
   const size_t smem = (size_t)width * sizeof(float);
   if (smem > 200 * 1024) return AB_BAD_ARG;
   const int threads = width >= 1024 ? 256 : 128;
@@ -296,8 +429,6 @@ AB_API int ab_post_norm_add(float* x, const void* a, const void* b, int in_dtype
     ab_launch(post_norm_add_kernel<TA, TO>, dim3((unsigned)n_rows), dim3(threads), smem, stream, x, (const TA*)a,       \
               (const TA*)b, wa, wb, w, w_next, (TO*)out, tok_seq, width, eps);                                          \
   }
-  const bool out_f32 = out == nullptr || out_dtype == AB_F32;
-  if (!out_f32 && out_dtype != AB_BF16) return AB_BAD_ARG;
   if (in_dtype == AB_F32) { if (out_f32) AB_GO(float, float) else AB_GO(float, bf16) }
   else if (in_dtype == AB_BF16) { if (out_f32) AB_GO(bf16, float) else AB_GO(bf16, bf16) }
   else return AB_BAD_ARG;

@@ -1558,6 +1558,8 @@ def talk_max_row() -> int:
 
 
 TALK_ON_TENSOR_CORES = True      # bfloat16 steps whose sizes the tile kernel takes run there
+TALK_DECODE_IN_PARTS = True      # steps of one token per sequence cut the keys into parts (`ab_talk_decode`)
+TALK_DECODE_BLOCKS = 296         # CTAs that such a step aims at: two per processor
 
 
 def attention_talk(q, q_stride, out, cache, ctx, H, G, Dk, Dv, scale, talk, gate_rows=None, gate_stride=0, window=0):
@@ -1569,7 +1571,7 @@ def attention_talk(q, q_stride, out, cache, ctx, H, G, Dk, Dv, scale, talk, gate
     token side by side); talk float32 [H, H]; gate_rows (or None): rows of `gate_stride` numbers of q's dtype whose
     first H*Dv are the gate's logits (sigmoid is applied); out [T, H*Dv] of q's dtype, heads in their own order.
     Every head's attention over all value heads is one float32 row A[t, x, G*Dv]; the mixing is a second kernel.
-    In bfloat16 with sizes in steps of 16 and G*Dv up to 256 the first is the tensor-core tile kernel."""
+    In bfloat16 with sizes in steps of 16 the first is the tensor-core tile kernel, 256 columns of A per launch."""
     k_pages, v_pages, table = cache.k, cache.v, cache.block_table
     _cuda(q, out, k_pages, v_pages, table, talk, gate_rows)
     T, W = ctx.n_tokens, G * Dv
@@ -1592,20 +1594,44 @@ def attention_talk(q, q_stride, out, cache, ctx, H, G, Dk, Dv, scale, talk, gate
               and gate_rows.numel() >= (T - 1) * gate_stride + H * Dv, "attention_talk: gate rows of q's dtype")
     _i32(ctx.tok_pos, T, "tok_pos")
     _i32(ctx.tok_seq, T, "tok_seq")
+    per = 8 if q.dtype == torch.bfloat16 else 4
+    if TALK_DECODE_IN_PARTS and ctx.is_decode and page == 64 and Dk % per == 0 and W % 4 == 0:
+        # one token per sequence: the keys in parts, so that few tokens fill the device.  The parts follow from the
+        # block table's width alone (a captured step stays valid while its sequences grow)
+        n_table = table.shape[1]
+        if window:
+            n_table = min(n_table, -(-int(window) // page) + 1)
+        per_part = T * G * -(-(H // G) // 4) * -(-W // 512)
+        parts = max(1, min(n_table, -(-TALK_DECODE_BLOCKS // per_part), 32))
+        pages_per_part = -(-n_table // parts)
+        parts = -(-n_table // pages_per_part)
+        A = torch.empty((q.shape[0] * parts, H * W), dtype=torch.float32, device=q.device)
+        ml = torch.empty((q.shape[0] * parts, H * 2), dtype=torch.float32, device=q.device)
+        lib = _lib("attention_maps")
+        _check(lib.ab_talk_decode(
+            _p(q), q_stride, _p(A), _p(ml), parts, pages_per_part, _dt(q), _p(k_pages), _p(v_pages), _p(table),
+            table.shape[1], _p(ctx.tok_pos), _p(ctx.tok_seq), T, H, G, Dk, Dv, page, ctypes.c_float(scale),
+            int(window or 0), _stream()), "talk_decode")
+        _check(lib.ab_talk_combine_parts(
+            _p(A), _p(ml), parts, _p(talk), _p(gate_rows), int(gate_stride), _p(out), _dt(out), _p(ctx.tok_seq), T, H, G,
+            Dv, _stream()), "talk_combine")
+        return out
     A = torch.empty((q.shape[0], H * W), dtype=torch.float32, device=q.device)
-    if (TALK_ON_TENSOR_CORES and page == 64
-            and attention_maps_mma_supports(H // G, 1, G, Dk, W, q_stride, q.dtype) and H // G <= 64):
-        # the tile kernel with the G key heads as the maps of one group whose value row is all heads' values
+    if (TALK_ON_TENSOR_CORES and page == 64 and W % 16 == 0
+            and attention_maps_mma_supports(H // G, 1, G, Dk, min(W, 256), q_stride, q.dtype) and H // G <= 64):
+        # the tile kernel with the G key heads as the maps of one group whose value row is all heads' values, 256
+        # columns of that row per launch
         _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
         if ctx.is_decode:
             tile_seq = tile_q0 = _row_index(q.device, T)
             n_tiles, tpt = T, 1
         else:
             tile_seq, tile_q0, n_tiles, tpt = _prefill_tiles(ctx, H // G, q.device)
-        _check(_lib("attention_mma").ab_attention_prefill_maps_bf16(
-            _p(q), q_stride, _p(A), 1, _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_pos),
-            _p(ctx.cu_q), _p(ctx.tok_seq), _p(tile_seq), _p(tile_q0), n_tiles, tpt, H, G, G, Dk, W,
-            ctypes.c_float(scale), int(window or 0), None, _stream()), "attention_prefill")
+        for col0 in range(0, W, 256):
+            _check(_lib("attention_mma").ab_attention_prefill_maps_cols_bf16(
+                _p(q), q_stride, _p(A), 1, _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_pos),
+                _p(ctx.cu_q), _p(ctx.tok_seq), _p(tile_seq), _p(tile_q0), n_tiles, tpt, H, G, G, Dk, min(256, W - col0),
+                ctypes.c_float(scale), int(window or 0), None, W, col0, _stream()), "attention_prefill")
     else:
         _check(_lib("attention_maps").ab_talk_attend(
             _p(q), q_stride, _p(A), _dt(q), _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_pos),

@@ -33,6 +33,9 @@ latent-attention layers, dense and routed feed-forwards) beside the Llama decode
 dense feed-forward: one prompt of 2,048 tokens and decode at batch 8 from 512-token prompts, at two sizes.
 `--design buguzen` does the same for the Buguzen decoder (linear attention with a fixed decay, attention with
 two score maps, attention over its own keys, token inputs, two layers that run twice).
+`--design sazepel` does the same for the Sazepel decoder (retention; attention with mixed heads beside a retention;
+routed gated experts in every layer), beside the Lefatar decoder (the framework's other decoder with routed experts
+and a matrix state per head) and the Llama decoder.
 
 One JSON line goes to standard output.  With --gpus N > 1 it prints a line that says so and exits
 with 2: this library runs on one GPU.
@@ -539,7 +542,7 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------------------------------------
-# --design lefatar | buguzen: that decoder beside the Llama decoder of the same width, depth and dense
+# --design lefatar | buguzen | sazepel: that decoder beside the Llama decoder of the same width, depth and dense
 # feed-forward, at sizes that resemble a real model's layers (random weights).
 
 def _lefatar_layers(E, mlstm, latent, dense_ff, moe, n_layers):
@@ -599,6 +602,24 @@ def _buguzen_config(z):
             "token_side": {"dim": b["side"]}}
 
 
+def _sazepel_config(z):
+    """Eight layers in the pattern (attention with mixed heads beside a retention, retention), every layer with routed
+    gated experts of the size of the Lefatar decoder's beside it."""
+    rt = z["moe"]["router"]
+    mlp = {"kind": "moe", "expert": dict(z["moe"]["expert"]), "router": {"experts": rt["experts"], "top": rt["top"]}}
+    lin = z["buguzen"]
+
+    def ret(heads):
+        return {"heads": heads, "dim": lin["lin_dim"], "vdim": lin["lin_vdim"], "decay": _decays(heads),
+                "rot": {"base": 1e6, "dims": lin["lin_dim"]}}
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head_dim"], "vdim": z["head_dim"],
+            "scale": z["head_dim"] ** -0.5}
+    pair = [{"type": "parallel", "mixer": {"left": left, "right": ret(lin["lin_heads"] // 2)}, "mlp": mlp},
+            {"type": "retention", "mixer": ret(lin["lin_heads"]), "mlp": mlp}]
+    return {"architecture": "Sazepel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "logit_scale": 1.0, "layers": [pair[i % 2] for i in range(z["layers"])]}
+
+
 def design_configs(size, design="lefatar"):
     z = DESIGN_SIZES[size]
     llama = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": z["layers"], "hidden_size": z["width"],
@@ -610,6 +631,8 @@ def design_configs(size, design="lefatar"):
         return {"buguzen": _buguzen_config(z), "llama": llama}
     lefatar = {"architecture": "Lefatar", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
                "layers": _lefatar_layers(z["width"], z["mlstm"], z["latent"], z["dense_ff"], z["moe"], z["layers"])}
+    if design == "sazepel":
+        return {"sazepel": _sazepel_config(z), "lefatar": lefatar, "llama": llama}
     return {"lefatar": lefatar, "llama": llama}
 
 
@@ -690,7 +713,7 @@ def main():
                     help="with --only decode: equal prompts of this many tokens instead of the workload's")
     ap.add_argument("--prefill-tokens", type=int, default=0,
                     help="with --only prefill: one prompt of this many tokens instead of the workload's")
-    ap.add_argument("--design", default="", choices=["", "lefatar", "buguzen"],
+    ap.add_argument("--design", default="", choices=["", "lefatar", "buguzen", "sazepel"],
                     help="instead of the benchmark workload: prefill and decode throughput of this design beside the "
                          "Llama decoder of the same width and depth (random weights), one JSON line")
     ap.add_argument("--size", default="", choices=[""] + sorted(DESIGN_SIZES), help="with --design: one size only")

@@ -193,6 +193,8 @@ MIXED_SHAPES = [
     # tensor-core tiles in bfloat16 (steps of 16, the values of all heads within 256) and ones that do not
     (4, 2, 16, 24), (8, 1, 32, 16), (3, 3, 20, 12), (1, 1, 24, 40), (6, 2, 48, 48), (8, 4, 64, 64), (2, 2, 72, 136),
     (6, 3, 16, 80), (4, 4, 128, 32),
+    # the values of all heads are more than 256 numbers: the tile kernel takes them 256 columns at a time
+    (8, 4, 32, 80), (4, 4, 16, 128), (3, 3, 48, 176),
 ]
 
 
@@ -236,12 +238,16 @@ def test_mixed_attention_whole_portions_and_single_tokens(dtype, H, G, D, V):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,D,V", [(4, 2, 16, 24), (4, 2, 32, 32), (2, 1, 20, 12)])
-@pytest.mark.parametrize("decode", [False, True])
-def test_mixed_attention_finds_a_key_far_back(dtype, H, G, D, V, decode):
+@pytest.mark.parametrize("decode", [False, True, "few parts"])
+def test_mixed_attention_finds_a_key_far_back(dtype, H, G, D, V, decode, monkeypatch):
     """One early token carries a key and a value that no other has; six hundred tokens (nine pages) later one
     token's queries ask for that key, with a scale that lets it outweigh the hundreds of others.  Only ONE head's
     queries ask; the mixing matrix spreads that head's weights to the others, each of which reads the planted value
-    from its own key/value head."""
+    from its own key/value head.  In decoding the ten pages of keys are taken one page per CTA, or ("few parts") in
+    runs of several pages per CTA."""
+    from alpacca_b200 import ops
+    if decode == "few parts":
+        monkeypatch.setattr(ops, "TALK_DECODE_BLOCKS", 3 * G)
     width, eps, scale = 40, 1e-6, 12.0
     part, w, mx = mixed_attention_part(dtype, width, H, G, D, V, scale, eps, seed=D, std=0.05, max_positions=1024)
     Wt = part.qkv.weight.float()
