@@ -602,82 +602,116 @@ talk_attend_kernel(TalkArgs a) {
 }
 
 // out[t, h, d] = gate * sum_g T[h, g] A[t, x(g), c(h)*Dv + d], x(g) = (g % R) * G + g / R, c(h) = h / R, R = H / G;
-// gate = sigmoid(gate_rows[t*gate_stride + h*Dv + d]) or 1.  A thread per column c*Dv + d of a token's rows of A: it
-// reads that column of all H rows once (neighbouring threads neighbouring addresses) and writes the R heads of
-// group c, four at a time.  The mixing matrix waits in shared memory (`talk_smem`: it fits).  With `ml`: A holds
-// `parts` partial rows per (token, x), [T, parts, H, W] sums of exp(score - m) * v with their (m, l) in
-// ml [T, parts, H, 2] (m in units of log2; a part without keys has l = 0): they are merged on the way.
-template <typename T>
+// gate = sigmoid(gate_rows[t*gate_stride + h*Dv + d]) or 1.  A thread per VEC neighbouring columns c*Dv + d of a
+// token's rows of A (VEC = 4 where Dv is a multiple of 4): it reads those columns of all H rows once (neighbouring
+// threads neighbouring addresses) and writes the R heads of group c, four at a time.  The mixing matrix and the
+// head that row x belongs to wait in shared memory (`talk_smem`: the matrix fits).
+template <typename T, int VEC>
 __global__ void __launch_bounds__(128)
-talk_combine_kernel(const float* __restrict__ A, const float* __restrict__ ml, int parts,
-                    const float* __restrict__ talk, const T* __restrict__ gate_rows, int gate_stride,
-                    T* __restrict__ out, const int* __restrict__ tok_seq, int n_tokens, int H, int G, int Dv,
-                    int talk_smem) {
-  extern __shared__ float tc_smem[];       // talk [H*H] (if talk_smem), then the parts' weights [parts*H] (if ml is given)
+talk_combine_kernel(const float* __restrict__ A, const float* __restrict__ talk, const T* __restrict__ gate_rows,
+                    int gate_stride, T* __restrict__ out, const int* __restrict__ tok_seq, int n_tokens, int H, int G,
+                    int Dv, int talk_smem) {
+  extern __shared__ float tc_smem[];       // head of row x [H] (as int), then talk [H*H] (if talk_smem)
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x;
   const int W = G * Dv, R = H / G;
-  const int col = blockIdx.y * blockDim.x + threadIdx.x;
+  const int col = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
   const bool live = tok_seq[t] >= 0;
-  float* wts = tc_smem + (talk_smem ? H * H : 0);
+  int* head_of = reinterpret_cast<int*>(tc_smem);
+  float* tks = tc_smem + H;
   if (live) {
+    for (int x = threadIdx.x; x < H; x += blockDim.x) head_of[x] = (x % G) * R + x / G;
     if (talk_smem)
-      for (int i = threadIdx.x; i < H * H; i += blockDim.x) tc_smem[i] = talk[i];
-    if (ml != nullptr) {
-      // weight of part p for row x: exp2(m_p - m) / sum over parts of l_p exp2(m_p - m)
-      for (int x = threadIdx.x; x < H; x += blockDim.x) {
-        const float* mlx = ml + ((size_t)t * parts * H + x) * 2;
-        float m = -INFINITY;
-        for (int p = 0; p < parts; ++p)
-          if (mlx[(size_t)p * H * 2 + 1] > 0.f) m = fmaxf(m, mlx[(size_t)p * H * 2]);
-        float l = 0.f;
-        for (int p = 0; p < parts; ++p) {
-          const float lp = mlx[(size_t)p * H * 2 + 1];
-          if (lp > 0.f) l += lp * exp2f(mlx[(size_t)p * H * 2] - m);
-        }
-        for (int p = 0; p < parts; ++p) {
-          const float lp = mlx[(size_t)p * H * 2 + 1];
-          wts[p * H + x] = (lp > 0.f && l > 0.f) ? exp2f(mlx[(size_t)p * H * 2] - m) / l : 0.f;
-        }
-      }
-    }
+      for (int i = threadIdx.x; i < H * H; i += blockDim.x) tks[i] = talk[i];
   }
   __syncthreads();
   if (col >= W) return;
   const int c = col / Dv, d = col - c * Dv;
   if (!live) {
-    for (int j = 0; j < R; ++j) out[((size_t)t * H + c * R + j) * Dv + d] = from_f32<T>(0.f);
+    for (int j = 0; j < R; ++j)
+      for (int v = 0; v < VEC; ++v) out[((size_t)t * H + c * R + j) * Dv + d + v] = from_f32<T>(0.f);
     return;
   }
-  const float* tk = talk_smem ? tc_smem : talk;
-  const float* At = A + (size_t)t * parts * H * W + col;
+  const float* tk = talk_smem ? tks : talk;
+  const float* At = A + (size_t)t * H * W + col;
   for (int j0 = 0; j0 < R; j0 += 4) {
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int x = 0; x < H; ++x) {
-      const int g = (x % G) * R + x / G;
-      float a;
-      if (ml != nullptr) {
-        a = 0.f;
-        for (int p = 0; p < parts; ++p) {
-          const float wp = wts[p * H + x];
-          if (wp != 0.f) a = fmaf(wp, At[((size_t)p * H + x) * W], a);
-        }
-      } else {
-        a = At[(size_t)x * W];
-      }
+    float acc[4][VEC];
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj)
-        if (j0 + jj < R) acc[jj] = fmaf(tk[(size_t)(c * R + j0 + jj) * H + g], a, acc[jj]);
+    for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) acc[jj][v] = 0.f;
+#pragma unroll 4
+    for (int x = 0; x < H; ++x) {
+      float a[VEC];
+      if (VEC == 4) {
+        const float4 raw = *reinterpret_cast<const float4*>(At + (size_t)x * W);
+        a[0] = raw.x; a[VEC > 1 ? 1 : 0] = raw.y; a[VEC > 2 ? 2 : 0] = raw.z; a[VEC > 3 ? 3 : 0] = raw.w;
+      } else {
+        a[0] = At[(size_t)x * W];
+      }
+      const int g = head_of[x];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const float w = j0 + jj < R ? tk[(size_t)(c * R + j0 + jj) * H + g] : 0.f;
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[jj][v] = fmaf(w, a[v], acc[jj][v]);
+      }
     }
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) {
       if (j0 + jj >= R) break;
       const int h = c * R + j0 + jj;
-      float sum = acc[jj];
-      if (gate_rows != nullptr) sum *= 1.0f / (1.0f + expf(-to_f32(gate_rows[(size_t)t * gate_stride + h * Dv + d])));
-      out[((size_t)t * H + h) * Dv + d] = from_f32<T>(sum);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) {
+        float sum = acc[jj][v];
+        if (gate_rows != nullptr)
+          sum *= 1.0f / (1.0f + expf(-to_f32(gate_rows[(size_t)t * gate_stride + h * Dv + d + v])));
+        out[((size_t)t * H + h) * Dv + d + v] = from_f32<T>(sum);
+      }
     }
+  }
+}
+
+// Merges the parts that `talk_decode` leaves: A[t, x, :] = sum_p w_p Ap[t, p, x, :] with w_p = exp2(m_p - m) / sum_p
+// l_p exp2(m_p - m), m the largest m_p (a part without keys has l = 0 and is left out).  A block per (token, x).
+__global__ void __launch_bounds__(128)
+talk_merge_kernel(const float* __restrict__ Ap, const float* __restrict__ ml, float* __restrict__ A, int parts, int H,
+                  int W) {
+  __shared__ float wts[64];
+  pdl_wait();
+  pdl_trigger();
+  const int x = blockIdx.x % H, t = blockIdx.x / H;
+  const float* mlx = ml + ((size_t)t * parts * H + x) * 2;
+  if (threadIdx.x < 32) {
+    float m = -INFINITY;
+    for (int p = threadIdx.x; p < parts; p += 32)
+      if (mlx[(size_t)p * H * 2 + 1] > 0.f) m = fmaxf(m, mlx[(size_t)p * H * 2]);
+    m = warp_max(m);
+    float l = 0.f;
+    for (int p = threadIdx.x; p < parts; p += 32) {
+      const float lp = mlx[(size_t)p * H * 2 + 1];
+      if (lp > 0.f) l += lp * exp2f(mlx[(size_t)p * H * 2] - m);
+    }
+    l = warp_sum(l);
+    for (int p = threadIdx.x; p < parts; p += 32) {
+      const float lp = mlx[(size_t)p * H * 2 + 1];
+      wts[p] = (lp > 0.f && l > 0.f) ? exp2f(mlx[(size_t)p * H * 2] - m) / l : 0.f;
+    }
+  }
+  __syncthreads();
+  const float* src = Ap + ((size_t)t * parts * H + x) * W;
+  float* dst = A + ((size_t)t * H + x) * W;
+  for (int col = threadIdx.x * 4; col < W; col += blockDim.x * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < parts; ++p) {
+      const float w = wts[p];
+      if (w != 0.f) {
+        const float4 v = *reinterpret_cast<const float4*>(src + (size_t)p * H * W + col);
+        acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+      }
+    }
+    *reinterpret_cast<float4*>(dst + col) = acc;
   }
 }
 
@@ -809,24 +843,32 @@ talk_decode_kernel(TalkArgs a, float* __restrict__ ml, int parts, int pages_per_
         acc[r][0] *= c0; acc[r][1] *= c0; acc[r][2] *= c0; acc[r][3] *= c0;
       }
       const T* vrow = vp + ((size_t)page * a.page_size) * W + col;
-#pragma unroll 4
-      for (int k = 0; k < n_keys; ++k) {
-        float v0, v1, v2, v3;
-        if (sizeof(T) == 2) {
-          const uint2 raw = *reinterpret_cast<const uint2*>(vrow + (size_t)k * W);
-          v0 = __uint_as_float(raw.x << 16); v1 = __uint_as_float(raw.x & 0xffff0000u);
-          v2 = __uint_as_float(raw.y << 16); v3 = __uint_as_float(raw.y & 0xffff0000u);
-        } else {
-          const float4 raw = *reinterpret_cast<const float4*>(vrow + (size_t)k * W);
-          v0 = raw.x; v1 = raw.y; v2 = raw.z; v3 = raw.w;
+      // the values of 16 keys are asked for at once (keys past the page's last have weight 0)
+      for (int k0 = 0; k0 < n_keys; k0 += 16) {
+        float4 vals[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          vals[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (k0 + i < n_keys) {
+            if (sizeof(T) == 2) {
+              const uint2 raw = *reinterpret_cast<const uint2*>(vrow + (size_t)(k0 + i) * W);
+              vals[i] = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                                    __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+            } else {
+              vals[i] = *reinterpret_cast<const float4*>(vrow + (size_t)(k0 + i) * W);
+            }
+          }
         }
 #pragma unroll
-        for (int r = 0; r < TD_RC; ++r) {
-          const float pk = ps[r * TD_KEYS + k];      // rows past nr hold what was there: their sums are not stored
-          acc[r][0] = fmaf(pk, v0, acc[r][0]);
-          acc[r][1] = fmaf(pk, v1, acc[r][1]);
-          acc[r][2] = fmaf(pk, v2, acc[r][2]);
-          acc[r][3] = fmaf(pk, v3, acc[r][3]);
+        for (int i = 0; i < 16; ++i) {
+#pragma unroll
+          for (int r = 0; r < TD_RC; ++r) {
+            const float pk = ps[r * TD_KEYS + k0 + i];      // rows past nr hold what was there: their sums are not stored
+            acc[r][0] = fmaf(pk, vals[i].x, acc[r][0]);
+            acc[r][1] = fmaf(pk, vals[i].y, acc[r][1]);
+            acc[r][2] = fmaf(pk, vals[i].z, acc[r][2]);
+            acc[r][3] = fmaf(pk, vals[i].w, acc[r][3]);
+          }
         }
       }
     }
@@ -883,33 +925,35 @@ AB_API int ab_talk_attend(const void* q, int q_stride, float* A, int dtype, cons
   return AB_BAD_ARG;
 }
 
-// `ml` given: A [T, parts, H, G*Dv] and ml [T, parts, H, 2] hold partial sums over parts of the keys (see the kernel);
-// without it parts is 1 and A holds the finished rows.
-AB_API int ab_talk_combine_parts(const float* A, const float* ml, int parts, const float* talk, const void* gate_rows,
-                                 int gate_stride, void* out, int dtype, const int* tok_seq, int n_tokens, int H, int G,
-                                 int Dv, cudaStream_t stream) {
+AB_API int ab_talk_combine(const float* A, const float* talk, const void* gate_rows, int gate_stride, void* out, int dtype,
+                           const int* tok_seq, int n_tokens, int H, int G, int Dv, cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
-  if (H <= 0 || G <= 0 || H % G || Dv <= 0 || parts < 1 || (parts > 1 && !ml) || !tok_seq) return AB_BAD_ARG;
+  if (H <= 0 || G <= 0 || H % G || Dv <= 0 || !tok_seq) return AB_BAD_ARG;
   const int W = G * Dv;
-  size_t smem = ml ? (size_t)parts * H * sizeof(float) : 0;
+  size_t smem = (size_t)H * sizeof(float);
   const int talk_smem = (size_t)H * H * sizeof(float) + smem <= 40 * 1024 ? 1 : 0;
   if (talk_smem) smem += (size_t)H * H * sizeof(float);
   if (smem > 48 * 1024) return AB_BAD_ARG;
-  dim3 grid((unsigned)n_tokens, (unsigned)((W + 127) / 128));
-  if (dtype == AB_F32)
-    ab_launch(talk_combine_kernel<float>, grid, dim3(128), smem, stream, A, ml, parts, talk, (const float*)gate_rows,
-              gate_stride, (float*)out, tok_seq, n_tokens, H, G, Dv, talk_smem);
-  else if (dtype == AB_BF16)
-    ab_launch(talk_combine_kernel<bf16>, grid, dim3(128), smem, stream, A, ml, parts, talk, (const bf16*)gate_rows,
-              gate_stride, (bf16*)out, tok_seq, n_tokens, H, G, Dv, talk_smem);
-  else
-    return AB_BAD_ARG;
+  const int vec = (Dv % 4 == 0) ? 4 : 1;
+  dim3 grid((unsigned)n_tokens, (unsigned)((W / vec + 127) / 128));
+#define AB_GO(T, VEC)                                                                                             \
+  ab_launch(talk_combine_kernel<T, VEC>, grid, dim3(128), smem, stream, A, talk, (const T*)gate_rows, gate_stride, \
+            (T*)out, tok_seq, n_tokens, H, G, Dv, talk_smem)
+  if (dtype == AB_F32) { if (vec == 4) AB_GO(float, 4); else AB_GO(float, 1); }
+  else if (dtype == AB_BF16) { if (vec == 4) AB_GO(bf16, 4); else AB_GO(bf16, 1); }
+  else return AB_BAD_ARG;
+#undef AB_GO
   return ab_launch_status();
 }
 
-AB_API int ab_talk_combine(const float* A, const float* talk, const void* gate_rows, int gate_stride, void* out, int dtype,
-                           const int* tok_seq, int n_tokens, int H, int G, int Dv, cudaStream_t stream) {
-  return ab_talk_combine_parts(A, nullptr, 1, talk, gate_rows, gate_stride, out, dtype, tok_seq, n_tokens, H, G, Dv, stream);
+// A[t, x, :] from the `parts` partial rows Ap [T, parts, H, W] and their (m, l) in ml [T, parts, H, 2]; W a multiple
+// of 4, up to 64 parts.
+AB_API int ab_talk_merge(const float* Ap, const float* ml, float* A, int parts, int n_tokens, int H, int W,
+                         cudaStream_t stream) {
+  if (n_tokens <= 0) return AB_OK;
+  if (parts < 1 || parts > 64 || H <= 0 || W <= 0 || W % 4 || (long long)n_tokens * H > 0x7fffffffLL) return AB_BAD_ARG;
+  ab_launch(talk_merge_kernel, dim3((unsigned)(n_tokens * H)), dim3(128), 0, stream, Ap, ml, A, parts, H, W);
+  return ab_launch_status();
 }
 
 // The decode form: one token per sequence, the keys in `parts` runs of `pages_per_part` pages (see the kernel).

@@ -1612,9 +1612,11 @@ def attention_talk(q, q_stride, out, cache, ctx, H, G, Dk, Dv, scale, talk, gate
             _p(q), q_stride, _p(A), _p(ml), parts, pages_per_part, _dt(q), _p(k_pages), _p(v_pages), _p(table),
             table.shape[1], _p(ctx.tok_pos), _p(ctx.tok_seq), T, H, G, Dk, Dv, page, ctypes.c_float(scale),
             int(window or 0), _stream()), "talk_decode")
-        _check(lib.ab_talk_combine_parts(
-            _p(A), _p(ml), parts, _p(talk), _p(gate_rows), int(gate_stride), _p(out), _dt(out), _p(ctx.tok_seq), T, H, G,
-            Dv, _stream()), "talk_combine")
+        merged = torch.empty((q.shape[0], H * W), dtype=torch.float32, device=q.device)
+        _check(lib.ab_talk_merge(_p(A), _p(ml), _p(merged), parts, T, H, W, _stream()), "talk_merge")
+        _check(lib.ab_talk_combine(
+            _p(merged), _p(talk), _p(gate_rows), int(gate_stride), _p(out), _dt(out), _p(ctx.tok_seq), T, H, G, Dv,
+            _stream()), "talk_combine")
         return out
     A = torch.empty((q.shape[0], H * W), dtype=torch.float32, device=q.device)
     if (TALK_ON_TENSOR_CORES and page == 64 and W % 16 == 0
