@@ -1560,6 +1560,7 @@ def talk_max_row() -> int:
 TALK_ON_TENSOR_CORES = True      # bfloat16 steps whose sizes the tile kernel takes run there
 TALK_DECODE_IN_PARTS = True      # steps of one token per sequence cut the keys into parts (`ab_talk_decode`)
 TALK_DECODE_BLOCKS = 296         # CTAs that such a step aims at: two per processor
+TALK_TILE_COLUMNS = 256          # columns of a token's value row that one launch of the tile kernel takes (a multiple of 16)
 
 
 def attention_talk(q, q_stride, out, cache, ctx, H, G, Dk, Dv, scale, talk, gate_rows=None, gate_stride=0, window=0):
@@ -1620,7 +1621,7 @@ def attention_talk(q, q_stride, out, cache, ctx, H, G, Dk, Dv, scale, talk, gate
         return out
     A = torch.empty((q.shape[0], H * W), dtype=torch.float32, device=q.device)
     if (TALK_ON_TENSOR_CORES and page == 64 and W % 16 == 0
-            and attention_maps_mma_supports(H // G, 1, G, Dk, min(W, 256), q_stride, q.dtype) and H // G <= 64):
+            and attention_maps_mma_supports(H // G, 1, G, Dk, min(W, TALK_TILE_COLUMNS), q_stride, q.dtype) and H // G <= 64):
         # the tile kernel with the G key heads as the maps of one group whose value row is all heads' values, 256
         # columns of that row per launch
         _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
@@ -1629,10 +1630,11 @@ def attention_talk(q, q_stride, out, cache, ctx, H, G, Dk, Dv, scale, talk, gate
             n_tiles, tpt = T, 1
         else:
             tile_seq, tile_q0, n_tiles, tpt = _prefill_tiles(ctx, H // G, q.device)
-        for col0 in range(0, W, 256):
+        for col0 in range(0, W, TALK_TILE_COLUMNS):
             _check(_lib("attention_mma").ab_attention_prefill_maps_cols_bf16(
                 _p(q), q_stride, _p(A), 1, _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_pos),
-                _p(ctx.cu_q), _p(ctx.tok_seq), _p(tile_seq), _p(tile_q0), n_tiles, tpt, H, G, G, Dk, min(256, W - col0),
+                _p(ctx.cu_q), _p(ctx.tok_seq), _p(tile_seq), _p(tile_q0), n_tiles, tpt, H, G, G, Dk,
+                min(TALK_TILE_COLUMNS, W - col0),
                 ctypes.c_float(scale), int(window or 0), None, W, col0, _stream()), "attention_prefill")
     else:
         _check(_lib("attention_maps").ab_talk_attend(
