@@ -185,16 +185,21 @@ __device__ __forceinline__ float sum_with_sink(float l, float m, const float* __
 // captured step of one token each).  DMAX covers both D and Dv.  The Dv columns may be a part of wider value rows:
 // a value row has `v_row` numbers of which this launch reads columns v_col0 .. v_col0 + Dv, and an output vector
 // has v_row numbers of which it writes the same columns (v_row = Dv, v_col0 = 0: all of it).
-template <int DMAX>
-__global__ void __launch_bounds__(128)
+// NG > 1: the CTA has NG groups of four warps; all groups take the same 64 rows and key tiles (each forms the scores
+// for itself) and group c the columns c*group_cols .. (c+1)*group_cols of the launch's Dv: one copy of the key tile
+// and of a value tile of all Dv columns serves NG times the warps, where a value row is too wide for one warp's
+// registers.  DMAX then covers D and group_cols.
+template <int DMAX, int NG>
+__global__ void __launch_bounds__(128 * NG)
 attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, void* __restrict__ out_any, int out_f32,
                          const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                          const int* __restrict__ block_table, int table_width, const int* __restrict__ tok_pos,
                          const int* __restrict__ cu_q, const int* __restrict__ tok_seq,
                          const int* __restrict__ tile_seq, const int* __restrict__ tile_q0, int H, int K, int M, int D,
                          int Dv, float scale_log2, int window, int tokens_per_tile, const float* __restrict__ sink,
-                         int v_row, int v_col0) {
+                         int v_row, int v_col0, int group_cols) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int NT = 128 * NG;
   const int pitch = D + 8, pitch_v = Dv + 8;
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);            // [64][pitch]
   bf16* kbuf = qs + 64 * pitch;                            // [2][64][pitch]
@@ -202,7 +207,10 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, void* __res
 
   pdl_wait();
   pdl_trigger();
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = NG == 1 ? tid >> 5 : (tid >> 5) & 3;       // which 16 of the 64 rows
+  const int col_first = NG == 1 ? 0 : (tid >> 7) * group_cols;  // this warp's columns of the launch's Dv
+  const int n_cols = NG == 1 ? Dv : min(group_cols, Dv - col_first);
   const int g = lane >> 2, t4 = lane & 3;
   const int G = H / K;
   // tile by tile (longest key ranges first), the KV heads of a tile side by side: CTAs start in index order
@@ -218,7 +226,7 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, void* __res
   // stage Q rows: row r = (token q0 + r / G, head kh*G + r % G); rows past the end are zero
   {
     const int cpr = D >> 3;
-    for (int c = tid; c < 64 * cpr; c += 128) {
+    for (int c = tid; c < 64 * cpr; c += NT) {
       const int r = c / cpr, cc = c - r * cpr;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (r < n_rows) {
@@ -245,8 +253,8 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, void* __res
   auto issue = [&](int kb, int stage) {
     const size_t base = ((size_t)bt[kb] * K + kh) * PAGE * D;
     const size_t base_v = ((size_t)bt[kb] * (K / M) + grp) * PAGE * v_row + v_col0;
-    load_tile_async(kbuf + stage * 64 * pitch, k_pages + base, D, pitch, tid, 128);
-    load_tile_async(vbuf + stage * 64 * pitch_v, v_pages + base_v, Dv, pitch_v, tid, 128, v_row);
+    load_tile_async(kbuf + stage * 64 * pitch, k_pages + base, D, pitch, tid, NT);
+    load_tile_async(vbuf + stage * 64 * pitch_v, v_pages + base_v, Dv, pitch_v, tid, NT, v_row);
     cp_async_commit();
   };
   issue(kb_begin, 0);
@@ -256,10 +264,10 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, void* __res
     __syncthreads();
     const int key0 = kb * PAGE;
     // rows of this warp that exist at all; a warp without rows still joins the barriers
-    if (warp * 16 < n_rows) {
+    if (warp * 16 < n_rows && n_cols > 0) {
       const bool need_mask = (key0 + PAGE - 1 > pos_first) || (window > 0);
-      attend_tile<DMAX>(st, qs + warp * 16 * pitch, kbuf + stage * 64 * pitch, vbuf + stage * 64 * pitch_v, pitch,
-                        pitch_v, D, Dv, scale_log2, key0, pos0, pos1, lo0, lo1, need_mask);
+      attend_tile<DMAX>(st, qs + warp * 16 * pitch, kbuf + stage * 64 * pitch, vbuf + stage * 64 * pitch_v + col_first,
+                        pitch, pitch_v, D, n_cols, scale_log2, key0, pos0, pos1, lo0, lo1, need_mask);
     }
     __syncthreads();
   }
@@ -273,11 +281,11 @@ attention_prefill_kernel(const bf16* __restrict__ qkv, int q_stride, void* __res
   if (r0 < n_rows) l0 = sum_with_sink(l0, st.m[0], sink, grp * G + r0 % G);
   if (r1 < n_rows) l1 = sum_with_sink(l1, st.m[1], sink, grp * G + r1 % G);
   const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
-  const size_t o0 = ((size_t)(q0 + r0 / G) * H + (grp * G + r0 % G) * M + map) * v_row + v_col0;
-  const size_t o1 = ((size_t)(q0 + r1 / G) * H + (grp * G + r1 % G) * M + map) * v_row + v_col0;
+  const size_t o0 = ((size_t)(q0 + r0 / G) * H + (grp * G + r0 % G) * M + map) * v_row + v_col0 + col_first;
+  const size_t o1 = ((size_t)(q0 + r1 / G) * H + (grp * G + r1 % G) * M + map) * v_row + v_col0 + col_first;
 #pragma unroll
   for (int dt = 0; dt < DMAX / 8; ++dt) {
-    if (dt * 8 < Dv) {
+    if (dt * 8 < n_cols) {
       const int d = dt * 8 + 2 * t4;
       if (out_f32) {
         float* out = reinterpret_cast<float*>(out_any);
@@ -707,41 +715,69 @@ AB_API int ab_attention_decode_round_pages(int D) { return ab_attention_decode_r
 // The general form (see the kernel): H query vectors, K key heads of D dims, K / M value heads of Dv dims.
 // `sink`: float [H / M] or null (see sum_with_sink); `tok_seq`: int [n_tokens] or null.
 // `v_row`, `v_col0`: columns v_col0 .. v_col0 + Dv of value rows and output vectors of v_row numbers (both multiples
-// of 8: 16-byte pieces).
+// of 8: 16-byte pieces).  `group_cols`: the columns of Dv that one group of four warps takes (a multiple of 16, up to
+// 256); ceil(Dv / group_cols) must be 1, 2 or 4 (four groups: D and group_cols up to 128).
+AB_API int ab_attention_prefill_maps_groups_bf16(const void* qkv, int q_stride, void* out, int out_f32,
+                                                 const void* k_pages, const void* v_pages, const int* block_table,
+                                                 int table_width, const int* tok_pos, const int* cu_q,
+                                                 const int* tok_seq, const int* tile_seq, const int* tile_q0, int n_tiles,
+                                                 int tokens_per_tile, int H, int K, int M, int D, int Dv, float scale,
+                                                 int window, const float* sink, int v_row, int v_col0, int group_cols,
+                                                 cudaStream_t stream) {
+  if (n_tiles <= 0) return AB_OK;
+  if (D <= 0 || D > 256 || (D % 16) || Dv <= 0 || (Dv % 16) || K <= 0 || H % K || K > 65535 || M <= 0 || K % M)
+    return AB_BAD_ARG;
+  if (group_cols <= 0 || group_cols > 256 || (group_cols % 16)) return AB_BAD_ARG;
+  const int groups = (Dv + group_cols - 1) / group_cols;
+  if (groups != 1 && groups != 2 && groups != 4) return AB_BAD_ARG;
+  if (v_col0 < 0 || v_col0 + Dv > v_row || (v_row % 8) || (v_col0 % 8)) return AB_BAD_ARG;
+  const int G = H / K;
+  if (tokens_per_tile < 1 || tokens_per_tile * G > 64) return AB_BAD_ARG;
+  const int pitch = D + 8, pitch_v = Dv + 8;
+  const size_t smem = ((size_t)(64 + 2 * 64) * pitch + (size_t)2 * 64 * pitch_v) * sizeof(bf16);
+  if (smem > 227 * 1024) return AB_BAD_ARG;
+  if ((long long)n_tiles * K > 0x7fffffffLL) return AB_BAD_ARG;
+  dim3 grid((unsigned)n_tiles * K);
+  const float sl = scale * LOG2E;
+#define AB_GO(DM, NG)                                                                                               \
+  {                                                                                                                 \
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DM, NG>,                                          \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
+    if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                              \
+    ab_launch(attention_prefill_kernel<DM, NG>, grid, dim3(128 * NG), smem, stream,                                 \
+        (const bf16*)qkv, q_stride, out, out_f32, (const bf16*)k_pages, (const bf16*)v_pages, block_table,          \
+        table_width, tok_pos, cu_q, tok_seq, tile_seq, tile_q0, H, K, M, D, Dv, sl, window, tokens_per_tile, sink,  \
+        v_row, v_col0, group_cols);                                                                                 \
+  }
+  const int widest = groups == 1 ? Dv : group_cols;
+  const int dm = dmax_of(D > widest ? D : widest);
+  if (groups == 1) {
+    switch (dm) {
+      case 64: AB_GO(64, 1); break;
+      case 128: AB_GO(128, 1); break;
+      default: AB_GO(256, 1); break;
+    }
+  } else if (groups == 2) {
+    if (dm <= 128) AB_GO(128, 2) else AB_GO(256, 2)
+  } else {
+    if (dm > 128) return AB_BAD_ARG;          // four groups of 256 columns: more registers than 512 threads have
+    AB_GO(128, 4)
+  }
+#undef AB_GO
+  return ab_launch_status();
+}
+
+// One group of warps: up to 256 columns per launch.
 AB_API int ab_attention_prefill_maps_cols_bf16(const void* qkv, int q_stride, void* out, int out_f32, const void* k_pages,
                                                const void* v_pages, const int* block_table, int table_width,
                                                const int* tok_pos, const int* cu_q, const int* tok_seq,
                                                const int* tile_seq, const int* tile_q0, int n_tiles, int tokens_per_tile,
                                                int H, int K, int M, int D, int Dv, float scale, int window,
                                                const float* sink, int v_row, int v_col0, cudaStream_t stream) {
-  if (n_tiles <= 0) return AB_OK;
-  if (D <= 0 || D > 256 || (D % 16) || Dv <= 0 || Dv > 256 || (Dv % 16) || K <= 0 || H % K || K > 65535 || M <= 0 || K % M)
-    return AB_BAD_ARG;
-  if (v_col0 < 0 || v_col0 + Dv > v_row || (v_row % 8) || (v_col0 % 8)) return AB_BAD_ARG;
-  const int G = H / K;
-  if (tokens_per_tile < 1 || tokens_per_tile * G > 64) return AB_BAD_ARG;
-  const int pitch = D + 8, pitch_v = Dv + 8;
-  const size_t smem = ((size_t)(64 + 2 * 64) * pitch + (size_t)2 * 64 * pitch_v) * sizeof(bf16);
-  if ((long long)n_tiles * K > 0x7fffffffLL) return AB_BAD_ARG;
-  dim3 grid((unsigned)n_tiles * K);
-  const float sl = scale * LOG2E;
-#define AB_GO(DM)                                                                                                  \
-  {                                                                                                                \
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DM>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                         (int)smem);                                                               \
-    if (e != cudaSuccess) return AB_CUDA_ERR + (int)e;                                                             \
-    ab_launch(attention_prefill_kernel<DM>, grid, dim3(128), smem, stream,                                         \
-        (const bf16*)qkv, q_stride, out, out_f32, (const bf16*)k_pages, (const bf16*)v_pages, block_table,         \
-        table_width, tok_pos, cu_q, tok_seq, tile_seq, tile_q0, H, K, M, D, Dv, sl, window, tokens_per_tile, sink, \
-        v_row, v_col0);                                                                                            \
-  }
-  switch (dmax_of(D > Dv ? D : Dv)) {
-    case 64: AB_GO(64); break;
-    case 128: AB_GO(128); break;
-    default: AB_GO(256); break;
-  }
-#undef AB_GO
-  return ab_launch_status();
+  if (Dv > 256) return AB_BAD_ARG;
+  return ab_attention_prefill_maps_groups_bf16(qkv, q_stride, out, out_f32, k_pages, v_pages, block_table, table_width,
+                                               tok_pos, cu_q, tok_seq, tile_seq, tile_q0, n_tiles, tokens_per_tile, H, K,
+                                               M, D, Dv, scale, window, sink, v_row, v_col0, Dv > 0 ? Dv : 16, stream);
 }
 
 AB_API int ab_attention_prefill_maps_bf16(const void* qkv, int q_stride, void* out, int out_f32, const void* k_pages,

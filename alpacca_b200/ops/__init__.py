@@ -1560,7 +1560,8 @@ def talk_max_row() -> int:
 TALK_ON_TENSOR_CORES = True      # bfloat16 steps whose sizes the tile kernel takes run there
 TALK_DECODE_IN_PARTS = True      # steps of one token per sequence cut the keys into parts (`ab_talk_decode`)
 TALK_DECODE_BLOCKS = 296         # CTAs that such a step aims at: two per processor
-TALK_TILE_COLUMNS = 256          # columns of a token's value row that one launch of the tile kernel takes (a multiple of 16)
+TALK_TILE_COLUMNS = 512          # columns of a token's value row that one launch of the tile kernel takes
+TALK_GROUP_COLUMNS = 256         # of which a group of four warps takes this many (1, 2 or 4 groups per CTA)
 
 
 def attention_talk(q, q_stride, out, cache, ctx, H, G, Dk, Dv, scale, talk, gate_rows=None, gate_stride=0, window=0):
@@ -1621,21 +1622,31 @@ def attention_talk(q, q_stride, out, cache, ctx, H, G, Dk, Dv, scale, talk, gate
         return out
     A = torch.empty((q.shape[0], H * W), dtype=torch.float32, device=q.device)
     if (TALK_ON_TENSOR_CORES and page == 64 and W % 16 == 0
-            and attention_maps_mma_supports(H // G, 1, G, Dk, min(W, TALK_TILE_COLUMNS), q_stride, q.dtype) and H // G <= 64):
-        # the tile kernel with the G key heads as the maps of one group whose value row is all heads' values, 256
-        # columns of that row per launch
+            and attention_maps_mma_supports(H // G, 1, G, Dk, min(W, TALK_GROUP_COLUMNS), q_stride, q.dtype)
+            and H // G <= 64):
+        # the tile kernel with the G key heads as the maps of one group whose value row is all heads' values; a launch
+        # takes as many columns of that row as shared memory holds beside the keys (two tiles of each in flight), in
+        # 1, 2 or 4 groups of warps
         _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
         if ctx.is_decode:
             tile_seq = tile_q0 = _row_index(q.device, T)
             n_tiles, tpt = T, 1
         else:
             tile_seq, tile_q0, n_tiles, tpt = _prefill_tiles(ctx, H // G, q.device)
-        for col0 in range(0, W, TALK_TILE_COLUMNS):
-            _check(_lib("attention_mma").ab_attention_prefill_maps_cols_bf16(
+        group = min(TALK_GROUP_COLUMNS, W)
+        room = (227 * 1024 // 2 - 192 * (Dk + 8)) // 128 - 8          # value columns that fit beside the keys
+        most = 4 if group <= 128 and Dk <= 128 else 2
+        per_launch = max(group, min(TALK_TILE_COLUMNS, most * group, room // group * group))
+        col0 = 0
+        while col0 < W:
+            cols = min(per_launch, W - col0)
+            if -(-cols // group) == 3:      # 1, 2 or 4 groups: a third group's columns wait for the next launch
+                cols = 2 * group
+            _check(_lib("attention_mma").ab_attention_prefill_maps_groups_bf16(
                 _p(q), q_stride, _p(A), 1, _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_pos),
-                _p(ctx.cu_q), _p(ctx.tok_seq), _p(tile_seq), _p(tile_q0), n_tiles, tpt, H, G, G, Dk,
-                min(TALK_TILE_COLUMNS, W - col0),
-                ctypes.c_float(scale), int(window or 0), None, W, col0, _stream()), "attention_prefill")
+                _p(ctx.cu_q), _p(ctx.tok_seq), _p(tile_seq), _p(tile_q0), n_tiles, tpt, H, G, G, Dk, cols,
+                ctypes.c_float(scale), int(window or 0), None, W, col0, group, _stream()), "attention_prefill")
+            col0 += cols
     else:
         _check(_lib("attention_maps").ab_talk_attend(
             _p(q), q_stride, _p(A), _dt(q), _p(k_pages), _p(v_pages), _p(table), table.shape[1], _p(ctx.tok_pos),

@@ -236,6 +236,25 @@ def test_mixed_attention_whole_portions_and_single_tokens(dtype, H, G, D, V):
     hs.cache.check()
 
 
+@pytest.mark.parametrize("group,most", [(128, 512), (128, 256), (64, 512), (256, 256), (48, 96)])
+@pytest.mark.parametrize("H,G,D,V", [(8, 4, 32, 80), (4, 4, 16, 128), (3, 3, 48, 176), (2, 2, 144, 96), (4, 1, 64, 32)])
+def test_mixed_attention_wide_value_rows_in_groups_of_warps(H, G, D, V, group, most, monkeypatch):
+    """The tile kernel takes a token's value row in launches of up to `most` columns, and within a launch 1, 2 or 4
+    groups of warps take `group` columns each: every split gives the same attention (bfloat16)."""
+    from alpacca_b200 import ops
+    monkeypatch.setattr(ops, "TALK_GROUP_COLUMNS", group)
+    monkeypatch.setattr(ops, "TALK_TILE_COLUMNS", most)
+    width, eps = 40, 1e-5
+    part, w, mx = mixed_attention_part("bfloat16", width, H, G, D, V, 3.0, eps, seed=H + V)
+    x, x64 = hidden(np.random.default_rng(D), 150, width, "bfloat16")
+    want = plain.talking_attention(x64, w, mx, eps)
+    hs = PartHarness([part.cache_spec()], "bfloat16", max_slots=2)
+    for cuts in ((150,), (70, 3, 77)):
+        s = hs.cache.alloc_slot()
+        close(feed(part, hs, s, x, cuts), want, "bfloat16", f"mixed attention, {group} of {most} columns", tol=(0.3, 0.03))
+        hs.cache.free_slot(s)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,D,V", [(4, 2, 16, 24), (4, 2, 32, 32), (2, 1, 20, 12)])
 @pytest.mark.parametrize("decode", [False, True, "few parts"])
