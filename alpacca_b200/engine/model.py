@@ -135,6 +135,14 @@ class DecoderModel(Part):
             return s.final_norm
         return None
 
+    def _plain_reader_after(self, i: int):
+        """The next block's first norm, if that block takes the norm's finished output from the block before it."""
+        s = self.spec
+        if i + 1 >= len(s.schedule) or s.schedule[i + 1].enter is not None:
+            return None
+        first = getattr(s.layers[s.schedule[i + 1].layer], "first_plain_norm", None)
+        return first() if first is not None else None
+
     def forward(self, ctx, cache) -> torch.Tensor:
         """Runs the step described by `ctx`; returns float32 logits [n_want, vocab]."""
         s = self.spec
@@ -146,8 +154,9 @@ class DecoderModel(Part):
             if run.enter is not None:
                 s.stream_parts[run.enter[0]].forward(stream, ctx, run.enter[1])
             stream.next_norm = self._reader_after(i, ctx)
+            stream.next_plain = self._plain_reader_after(i)
             s.layers[run.layer].forward(stream, ctx, view, write_cache=run.reads_entry_of is None)
-        stream.next_norm = None
+        stream.next_norm = stream.next_plain = None
         if ctx.n_want == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=stream.residual.device)
         if stream.owed is not None:

@@ -25,6 +25,9 @@ class HiddenStream:
     owed: OwedNorm | None = None       # or: the residual is up to date and these rows stand for `owed.norm`
     next_norm: Norm | None = None      # set by the model: the norm that reads the stream after this block,
                                        # if its reader accepts an OwedNorm in this step
+    next_plain: Norm | None = None     # set by the model: the next block's first norm, if that block takes the
+                                       # norm's finished output from the block before it (`ready`)
+    ready: tuple | None = None         # (norm, rows): the residual is up to date and `rows` are norm(residual)
 
 
 class PreNormBlock(Block):
@@ -84,7 +87,9 @@ class SandwichBlock(Block):
     the next norm's kernel as it is: one kernel norms it, adds it to the float32 stream and, between the two
     sub-layers, leaves the next norm's output as well (`ops.post_norm_add`).  A mixer may return a `HalfSum`
     (two mixers side by side whose normed outputs are averaged); the same kernel forms it.  The norms are
-    `RMSNorm`s (weight per column, eps), 32-bit arithmetic."""
+    `RMSNorm`s (weight per column, eps), 32-bit arithmetic.  Where the next block is of this kind too, the kernel
+    after this block's last sub-layer leaves that block's first norm as well (`first_plain_norm`,
+    `HiddenStream.ready`)."""
 
     def __init__(self, norm1: Norm, mixer: Mixer, post1: Norm, norm2: Norm | None = None,
                  ffn: FeedForward | None = None, post2: Norm | None = None):
@@ -99,16 +104,29 @@ class SandwichBlock(Block):
             return several()
         return super().cache_specs()
 
+    def first_plain_norm(self):
+        """The norm whose finished output this block takes from the kernel that ended the block before it."""
+        return self.norm1
+
     def forward(self, stream: HiddenStream, ctx, cache, write_cache: bool = True) -> None:
         stream.next_norm = None
-        h = _normed(self.norm1, stream)
+        after, stream.next_plain = stream.next_plain, None
+        ready, stream.ready = stream.ready, None
+        if ready is not None and ready[0] is self.norm1:
+            h = ready[1]
+        else:
+            h = _normed(self.norm1, stream)
         stream.delta = None
         y = self.mixer.forward(h, ctx, cache, write_cache)
-        if self.ffn is None:
-            _post_add(self.post1, stream.residual, y, ctx)
-            return
-        h = _post_add(self.post1, stream.residual, y, ctx, then=self.norm2)
-        _post_add(self.post2, stream.residual, self.ffn.forward(h, ctx), ctx)
+        last = self.post1 if self.ffn is None else self.post2
+        if after is not None and not (hasattr(after, "weight") and getattr(after, "eps", None) == last.eps):
+            after = None
+        if self.ffn is not None:
+            h = _post_add(self.post1, stream.residual, y, ctx, then=self.norm2)
+            y = self.ffn.forward(h, ctx)
+        rows = _post_add(last, stream.residual, y, ctx, then=after)
+        if after is not None:
+            stream.ready = (after, rows)
 
 
 def _post_add(post: Norm, residual, y, ctx, then: Norm | None = None):
