@@ -776,6 +776,22 @@ talk_decode_kernel(TalkArgs a, float* __restrict__ ml, int parts, int pages_per_
     const int page = bt[pg];
     const int key0 = pg * a.page_size;
     const int n_keys = min(a.page_size, pos - key0 + 1);
+    {
+      // ask the L2 for what comes after the scores: this page's value rows (the CTA's columns), and the next
+      // page's keys, 128 bytes per request
+      const int first = cb * TD_COLS, n_col = min(TD_COLS, W - first);
+      const int lines = (n_col * (int)sizeof(T) + 127) / 128;
+      const char* vbase = reinterpret_cast<const char*>(vp + ((size_t)page * a.page_size) * W + first);
+      for (int i = tid; i < n_keys * lines; i += 128) {
+        const int k = i / lines, ln = i - k * lines;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(vbase + (size_t)k * W * sizeof(T) + (size_t)ln * 128));
+      }
+      if (pg + 1 < page1) {
+        const char* kbase = reinterpret_cast<const char*>(kp + ((size_t)bt[pg + 1] * a.G + kh) * a.page_size * Dk);
+        const int kbytes = min(a.page_size, pos - key0 - a.page_size + 1) * Dk * (int)sizeof(T);
+        for (int i = tid * 128; i < kbytes; i += 128 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(kbase + i));
+      }
+    }
     __syncthreads();                          // the tile and the weights of the page before are done with
     {
       // the page's keys of head kh, 16 bytes at a time
