@@ -224,12 +224,16 @@ __global__ void moe_down_pairs_kernel(const T* __restrict__ act, const T* __rest
   const long long id = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (id >= (long long)n_tokens * width) return;
   const int t = (int)(id / width), i = (int)(id - (long long)t * width);
+  // a lane adds up its share of all chosen experts' rows, weighted; one sum over the warp at the end, so that the
+  // rows of different experts are asked for together
   float total = 0.f;
+#pragma unroll 4
   for (int k = 0; k < top; ++k) {
     const int e = idx[(size_t)t * top + k];
     const float part = lane_dot(act + ((size_t)t * top + k) * ff, w_down + ((size_t)i * E + e) * ff, ff, lane);
-    total += wts[(size_t)t * top + k] * warp_sum(part);
+    total = fmaf(wts[(size_t)t * top + k], part, total);
   }
+  total = warp_sum(total);
   if (lane == 0) out[(size_t)t * width + i] = from_f32<T>(total);
 }
 
