@@ -62,7 +62,8 @@ AB_API int ab_latent_prep(const float* x, int ld, int Q, int C, int R, const flo
                           const int* block_table, int table_width, int page_size, void* pages, void* cq_out,
                           int dtype, int n_tokens, int write_cache, cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
-  if (Q <= 0 || C <= 0 || R < 0 || n_rot < 0 || n_rot > R || (n_rot & 1) || ld < Q + C + R) return AB_BAD_ARG;
+  // a caller that writes no cache (a layer that reads another layer's latent) gives rows of the Q numbers alone
+  if (Q <= 0 || C <= 0 || R < 0 || n_rot < 0 || n_rot > R || (n_rot & 1) || ld < (write_cache ? Q + C + R : Q)) return AB_BAD_ARG;
   if (dtype == AB_F32)
     ab_launch(latent_prep_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, x, ld, Q, C, R, wq, wc, eps, cos_t, sin_t,
               n_rot, tok_pos, tok_seq, block_table, table_width, page_size, (float*)pages, (float*)cq_out, write_cache);
@@ -159,7 +160,8 @@ __global__ void latent_attention_simt_kernel(const float* __restrict__ q, float*
                                              const TC* __restrict__ pages, const int* __restrict__ block_table,
                                              int table_width, const int* __restrict__ tok_pos,
                                              const int* __restrict__ tok_seq, const float* __restrict__ sink,
-                                             int n_tokens, int H, int C, int R, int page_size, float scale) {
+                                             int n_tokens, int H, int C, int R, int page_size, float scale,
+                                             int window) {
   pdl_wait();
   pdl_trigger();
   const int lane = threadIdx.x & 31;
@@ -180,7 +182,7 @@ __global__ void latent_attention_simt_kernel(const float* __restrict__ q, float*
   }
   float m = -INFINITY, l = 0.f;
   const int* bt = block_table + (size_t)b * table_width;
-  for (int s = 0; s <= pos; ++s) {
+  for (int s = window > 0 ? max(0, pos - window + 1) : 0; s <= pos; ++s) {
     const int page = bt[s / page_size];
     const TC* kv = pages + ((size_t)page * page_size + (s % page_size)) * Dk;
     float kr[DPL];
@@ -217,7 +219,7 @@ __global__ void latent_attention_simt_kernel(const float* __restrict__ q, float*
 template <typename TC>
 static int latent_simt_go(const float* q, float* out, const void* pages, const int* block_table, int table_width,
                           const int* tok_pos, const int* tok_seq, const float* sink, int n_tokens, int H, int C, int R,
-                          int page_size, float scale, cudaStream_t stream) {
+                          int page_size, float scale, int window, cudaStream_t stream) {
   const long long warps = (long long)n_tokens * H;
   const int wpb = 4;
   const unsigned blocks = (unsigned)((warps + wpb - 1) / wpb);
@@ -225,7 +227,7 @@ static int latent_simt_go(const float* q, float* out, const void* pages, const i
 #define AB_GO(DPL)                                                                                                \
   latent_attention_simt_kernel<TC, DPL><<<blocks, wpb * 32, 0, stream>>>(q, out, (const TC*)pages, block_table,   \
                                                                          table_width, tok_pos, tok_seq, sink,    \
-                                                                         n_tokens, H, C, R, page_size, scale)
+                                                                         n_tokens, H, C, R, page_size, scale, window)
   if (dpl <= 1) AB_GO(1);
   else if (dpl <= 2) AB_GO(2);
   else if (dpl <= 4) AB_GO(4);
@@ -237,17 +239,26 @@ static int latent_simt_go(const float* q, float* out, const void* pages, const i
   return ab_launch_status();
 }
 
+// `window` > 0: a token sees itself and the window - 1 tokens before it
+AB_API int ab_latent_attention_simt_window(const float* q, float* out, const void* pages, int dtype,
+                                           const int* block_table, int table_width, const int* tok_pos,
+                                           const int* tok_seq, const float* sink, int n_tokens, int H, int C, int R,
+                                           int page_size, float scale, int window, cudaStream_t stream) {
+  if (n_tokens <= 0) return AB_OK;
+  if (H <= 0 || C <= 0 || R < 0 || C + R > 1024 || window < 0) return AB_BAD_ARG;
+  if (dtype == AB_F32)
+    return latent_simt_go<float>(q, out, pages, block_table, table_width, tok_pos, tok_seq, sink, n_tokens, H, C, R,
+                                 page_size, scale, window, stream);
+  if (dtype == AB_BF16)
+    return latent_simt_go<bf16>(q, out, pages, block_table, table_width, tok_pos, tok_seq, sink, n_tokens, H, C, R,
+                                page_size, scale, window, stream);
+  return AB_BAD_ARG;
+}
+
 AB_API int ab_latent_attention_simt(const float* q, float* out, const void* pages, int dtype, const int* block_table,
                                     int table_width, const int* tok_pos, const int* tok_seq, const float* sink,
                                     int n_tokens, int H, int C, int R, int page_size, float scale,
                                     cudaStream_t stream) {
-  if (n_tokens <= 0) return AB_OK;
-  if (H <= 0 || C <= 0 || R < 0 || C + R > 1024) return AB_BAD_ARG;
-  if (dtype == AB_F32)
-    return latent_simt_go<float>(q, out, pages, block_table, table_width, tok_pos, tok_seq, sink, n_tokens, H, C, R,
-                                 page_size, scale, stream);
-  if (dtype == AB_BF16)
-    return latent_simt_go<bf16>(q, out, pages, block_table, table_width, tok_pos, tok_seq, sink, n_tokens, H, C, R,
-                                page_size, scale, stream);
-  return AB_BAD_ARG;
+  return ab_latent_attention_simt_window(q, out, pages, dtype, block_table, table_width, tok_pos, tok_seq, sink, n_tokens,
+                                         H, C, R, page_size, scale, 0, stream);
 }

@@ -184,6 +184,124 @@ AB_API int ab_moe_route(const void* h, int dtype, int ld, const float* wr, int n
   return ab_moe_route_bias(h, dtype, ld, wr, nullptr, n_tokens, width, E, groups, keep, top, scale, z, idx, wts, stream);
 }
 
+// The choice from scores that are not a softmax, one warp per token, from the logits z [T, E]:
+//   s = sigmoid(z) (score_fn 1) or z itself (0);  the CHOICE is made by c = s + correction (if given), the weights
+//   are the chosen experts' s, times `scale`, divided by their sum if `renorm`.
+//   Groups: a group's score is the sum of its `group_top` largest c; experts outside the `keep` best groups cannot be
+//   chosen whatever their c (choice scores may be negative, so they are struck out with minus infinity).
+// The lower index wins a tie, among groups and among experts.
+__global__ void moe_route_scores_kernel(const float* __restrict__ z, const float* __restrict__ correction, int n_tokens,
+                                        int E, int groups, int keep, int group_top, int top, int score_fn, int renorm,
+                                        float scale, int* __restrict__ idx, float* __restrict__ wts) {
+  extern __shared__ float sm[];           // per warp: E scores, E choice scores, `groups` group scores
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + wib;
+  if (t >= n_tokens) return;
+  float* s = sm + (size_t)wib * (2 * E + groups);
+  float* c = s + E;
+  float* gs = c + E;
+  for (int e = lane; e < E; e += 32) {
+    const float v = z[(size_t)t * E + e];
+    const float sc = score_fn == 1 ? 1.0f / (1.0f + expf(-v)) : v;
+    s[e] = sc;
+    c[e] = sc + (correction != nullptr ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  const int per = E / groups;
+  if (keep < groups) {
+    for (int g = lane; g < groups; g += 32) {
+      // the sum of the group's `group_top` largest choice scores, by repeated arg-max over a few members
+      float total = 0.f;
+      unsigned long long taken_lo = 0, taken_hi = 0;      // members already counted (a group of up to 128)
+      for (int pick = 0; pick < group_top && pick < per; ++pick) {
+        float best = -INFINITY;
+        int bj = -1;
+        for (int j = 0; j < per; ++j) {
+          const bool used = j < 64 ? (taken_lo >> j) & 1ull : (taken_hi >> (j - 64)) & 1ull;
+          if (!used && (bj < 0 || c[g * per + j] > best)) { best = c[g * per + j]; bj = j; }
+        }
+        if (bj < 64) taken_lo |= 1ull << bj; else taken_hi |= 1ull << (bj - 64);
+        total += best;
+      }
+      gs[g] = total;
+    }
+    __syncwarp();
+    for (int pick = 0; pick < keep; ++pick) {
+      float best = -INFINITY;
+      int bg = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32)
+        if (!isnan(gs[g]) && (bg == 0x7fffffff || gs[g] > best)) { best = gs[g]; bg = g; }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int og = __shfl_xor_sync(0xffffffffu, bg, o);
+        if (og != 0x7fffffff && (bg == 0x7fffffff || ob > best || (ob == best && og < bg))) { best = ob; bg = og; }
+      }
+      if (lane == 0 && bg != 0x7fffffff) gs[bg] = __int_as_float(0x7fc00000);      // kept: marked with a NaN
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (!isnan(gs[e / per])) c[e] = -INFINITY;
+    __syncwarp();
+  }
+  float chosen_sum = 0.f;
+  for (int pick = 0; pick < top; ++pick) {
+    float best = -INFINITY;
+    int be = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = c[e];
+      if (v > best) { best = v; be = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
+    }
+    if (be == 0x7fffffff) be = 0;                      // nothing left to choose (or the row holds no numbers)
+    const float w = s[be];
+    chosen_sum += w;
+    if (lane == 0) {
+      idx[(size_t)t * top + pick] = be;
+      wts[(size_t)t * top + pick] = w;
+    }
+    __syncwarp();
+    if (lane == 0) c[be] = -INFINITY;                  // taken
+    __syncwarp();
+  }
+  if (lane == 0) {
+    const float f = renorm ? scale / (chosen_sum + 1e-20f) : scale;
+    for (int j = 0; j < top; ++j) wts[(size_t)t * top + j] *= f;
+  }
+}
+
+AB_API int ab_moe_route_scores(const void* h, int dtype, int ld, const float* wr, const float* bias, const float* correction,
+                               int n_tokens, int width, int E, int groups, int keep, int group_top, int top, int score_fn,
+                               int renorm, float scale, float* z, int* idx, float* wts, cudaStream_t stream) {
+  if (n_tokens <= 0) return AB_OK;
+  if (E <= 0 || E > MOE_MAX_EXPERTS || groups <= 0 || E % groups || keep <= 0 || keep > groups || top <= 0 ||
+      top > keep * (E / groups) || group_top <= 0 || E / groups > 128 || score_fn < 0 || score_fn > 1)
+    return AB_BAD_ARG;
+  const int wpb = 4;
+  const long long lw = (long long)n_tokens * E;
+  const unsigned lblocks = (unsigned)((lw + 7) / 8);
+  if (dtype == AB_F32)
+    ab_launch(moe_logits_kernel<float>, dim3(lblocks), dim3(256), 0, stream, (const float*)h, ld, wr, n_tokens, width, E, z, bias);
+  else if (dtype == AB_BF16)
+    ab_launch(moe_logits_kernel<bf16>, dim3(lblocks), dim3(256), 0, stream, (const bf16*)h, ld, wr, n_tokens, width, E, z, bias);
+  else
+    return AB_BAD_ARG;
+  int rc = ab_launch_status();
+  if (rc) return rc;
+  const unsigned blocks = (unsigned)((n_tokens + wpb - 1) / wpb);
+  const size_t smem = (size_t)wpb * (2 * E + groups) * sizeof(float);
+  ab_launch(moe_route_scores_kernel, dim3(blocks), dim3(wpb * 32), smem, stream, (const float*)z, correction, n_tokens, E,
+            groups, keep, group_top, top, score_fn, renorm, scale, idx, wts);
+  return ab_launch_status();
+}
+
 __device__ __forceinline__ float gelu_erf(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f)); }
 __device__ __forceinline__ float silu(float z) { return z / (1.0f + expf(-z)); }
 

@@ -435,3 +435,97 @@ AB_API int ab_post_norm_add(float* x, const void* a, const void* b, int in_dtype
 #undef AB_GO
   return ab_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// embed_pairs: the stream's first value for a model whose embedding has a factor and a hashed table of (previous
+// token, token) pairs:  x[t] = table[token_t] * scale + pairs[(prev_t * mul_prev + token_t * mul_cur) mod buckets],
+// and row `buckets` (the last one) of `pairs` for a sequence's first token.  The previous token of a step's first
+// token is what the sequence keeps from its last step: `last_token[slot]`, which the block of that first token
+// reads and then sets to the step's last token of the sequence (one thread does both, in this order).
+// A block per token; rows without a sequence become zero.
+template <typename T>
+__global__ void embed_pairs_kernel(const T* __restrict__ table, float scale, const T* __restrict__ pairs, long long buckets,
+                                   long long mul_prev, long long mul_cur, const int* __restrict__ tokens,
+                                   const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                   const int* __restrict__ cu_q, const int* __restrict__ slots,
+                                   int* __restrict__ last_token, float* __restrict__ out, int width) {
+  __shared__ long long pair_row;
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int b = tok_seq[t];
+  float* o = out + (size_t)t * width;
+  if (b < 0) {
+    for (int j = threadIdx.x; j < width; j += blockDim.x) o[j] = 0.f;
+    return;
+  }
+  const int tok = tokens[t];
+  if (pairs != nullptr) {
+    if (threadIdx.x == 0) {
+      const int first = cu_q[b];
+      long long row = buckets;
+      if (tok_pos[t] > 0) {
+        const long long prev = t > first ? tokens[t - 1] : last_token[slots[b]];
+        row = (prev * mul_prev + (long long)tok * mul_cur) % buckets;
+      }
+      if (t == first) last_token[slots[b]] = tokens[cu_q[b + 1] - 1];
+      pair_row = row;
+    }
+    __syncthreads();
+  }
+  const T* e = table + (size_t)tok * width;
+  if (pairs == nullptr) {
+    for (int j = threadIdx.x; j < width; j += blockDim.x) o[j] = to_f32(e[j]) * scale;
+    return;
+  }
+  const T* p = pairs + (size_t)pair_row * width;
+  for (int j = threadIdx.x; j < width; j += blockDim.x) o[j] = to_f32(e[j]) * scale + to_f32(p[j]);
+}
+
+AB_API int ab_embed_pairs(const void* table, int dtype, float scale, const void* pairs, long long buckets,
+                          long long mul_prev, long long mul_cur, const int* tokens, const int* tok_seq, const int* tok_pos,
+                          const int* cu_q, const int* slots, int* last_token, float* out, int n_tokens, int width,
+                          cudaStream_t stream) {
+  if (n_tokens <= 0 || width <= 0) return AB_OK;
+  if (!table || !tokens || !tok_seq || !out) return AB_BAD_ARG;
+  if (pairs && (!tok_pos || !cu_q || !slots || !last_token || buckets <= 0 || mul_prev < 0 || mul_cur < 0)) return AB_BAD_ARG;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (dtype == AB_F32)
+    ab_launch(embed_pairs_kernel<float>, dim3((unsigned)n_tokens), dim3(threads), 0, stream, (const float*)table, scale,
+              (const float*)pairs, buckets, mul_prev, mul_cur, tokens, tok_seq, tok_pos, cu_q, slots, last_token, out, width);
+  else if (dtype == AB_BF16)
+    ab_launch(embed_pairs_kernel<bf16>, dim3((unsigned)n_tokens), dim3(threads), 0, stream, (const bf16*)table, scale,
+              (const bf16*)pairs, buckets, mul_prev, mul_cur, tokens, tok_seq, tok_pos, cu_q, slots, last_token, out, width);
+  else
+    return AB_BAD_ARG;
+  return ab_launch_status();
+}
+
+// head_gate: y[t, h, :] *= sigmoid(g[t * g_stride + h]): one gate per head and token, 32-bit arithmetic
+template <typename T, typename TG>
+__global__ void head_gate_kernel(T* __restrict__ y, const TG* __restrict__ g, int g_stride, size_t total, int H, int V) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t th = i / V;
+  const size_t t = th / H;
+  const float z = to_f32(g[t * g_stride + (th - t * H)]);
+  y[i] = from_f32<T>(to_f32(y[i]) / (1.0f + expf(-z)));
+}
+
+AB_API int ab_head_gate(void* y, int dtype, const void* g, int g_dtype, int g_stride, int n_tokens, int H, int V,
+                        cudaStream_t stream) {
+  if (n_tokens <= 0 || H <= 0 || V <= 0) return AB_OK;
+  if (!y || !g || g_stride < H) return AB_BAD_ARG;
+  const size_t total = (size_t)n_tokens * H * V;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+#define AB_GO(T, TG) ab_launch(head_gate_kernel<T, TG>, dim3(blocks), dim3(256), 0, stream, (T*)y, (const TG*)g, g_stride, total, H, V)
+  if (dtype == AB_F32 && g_dtype == AB_F32) AB_GO(float, float);
+  else if (dtype == AB_BF16 && g_dtype == AB_BF16) AB_GO(bf16, bf16);
+  else if (dtype == AB_BF16 && g_dtype == AB_F32) AB_GO(bf16, float);
+  else if (dtype == AB_F32 && g_dtype == AB_BF16) AB_GO(float, bf16);
+  else return AB_BAD_ARG;
+#undef AB_GO
+  return ab_launch_status();
+}

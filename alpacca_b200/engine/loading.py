@@ -46,9 +46,13 @@ def build_model(config: ModelConfig | dict, dtype=torch.bfloat16, device="cuda",
 def load_model_dir(model_dir, dtype=torch.bfloat16, device="cuda", max_positions: int | None = None) -> DecoderModel:
     """config.json chooses the model class; model.safetensors is read by tensor name."""
     config = load_config(model_dir)
-    model = build_model(config, dtype, device, max_positions)
     source = FolderSource(model_dir)
     try:
+        # sizes that config.json leaves to the tensors' shapes (an architecture that has such answers `with_shapes`)
+        complete = getattr(config, "with_shapes", None)
+        if complete is not None:
+            config = complete({name: tuple(shape) for name, (_, shape) in source.table().items()})
+        model = build_model(config, dtype, device, max_positions)
         model.load_weights(source, where=str(model_dir))
     finally:
         source.close()

@@ -83,6 +83,13 @@ class DecoderModel(Part):
             specs = block_cache_specs(spec.layers[r.layer])
             self.entries_of_run.append(list(range(len(self._entry_specs), len(self._entry_specs) + len(specs))))
             self._entry_specs.extend(specs)
+        # an embedding that keeps something per sequence (its last token, say) has an entry after the runs'
+        own = getattr(spec.embedding, "cache_spec", None)
+        own = own() if own is not None else None
+        self.embedding_entry = None
+        if own is not None:
+            self.embedding_entry = len(self._entry_specs)
+            self._entry_specs.append(own)
 
     def children(self):
         s = self.spec
@@ -146,7 +153,13 @@ class DecoderModel(Part):
     def forward(self, ctx, cache) -> torch.Tensor:
         """Runs the step described by `ctx`; returns float32 logits [n_want, vocab]."""
         s = self.spec
-        stream = HiddenStream(s.embedding.forward(ctx.tokens, ctx.n_tokens))
+        if self.embedding_entry is not None:
+            kept = cache.entry_view(self.embedding_entry, ctx.block_tables)
+            stream = HiddenStream(s.embedding.forward(ctx.tokens, ctx.n_tokens, ctx=ctx, cache=kept))
+        elif getattr(s.embedding, "scale", 1.0) != 1.0:
+            stream = HiddenStream(s.embedding.forward(ctx.tokens, ctx.n_tokens, ctx=ctx))
+        else:
+            stream = HiddenStream(s.embedding.forward(ctx.tokens, ctx.n_tokens))
         if s.position is not None:
             s.position.add_to_embeddings(stream.residual, ctx)
         for i, run in enumerate(s.schedule):

@@ -1,2 +1,2 @@
 """The built-in architectures; importing this package registers them."""
-from . import buguzen, lefatar, llama, sazepel  # noqa: F401
+from . import buguzen, lefatar, llama, mavidra, sazepel  # noqa: F401

@@ -980,11 +980,14 @@ def latent_prep(x, Q, C, R, q_norm_weight, c_norm_weight, eps, rot, ctx, cache, 
     cos, sin, n_rot, pairing = rot if rot is not None else (None, None, 0, 0)
     _cuda(x, q_norm_weight, c_norm_weight, cos, sin, pages, table, cq_out)
     T = ctx.n_tokens
-    _need(x.dtype == torch.float32 and x.is_contiguous() and x.shape[-1] >= Q + C + R and x.numel() >= T * x.shape[-1],
-          "latent_prep: x must be contiguous float32 [T, Q + C + R]")
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.shape[-1] >= (Q + C + R if write_cache else Q)
+          and x.numel() >= T * x.shape[-1], "latent_prep: x must be contiguous float32 [T, Q + C + R] ([T, Q] for a "
+          "caller that writes no cache)")
     _need(pairing == 0, "latent_prep rotates pairs (2i, 2i+1) only")
     _need(n_rot <= R, f"latent_prep: {n_rot} rotated dims, the rotated part has {R}")
     for wt, n in ((q_norm_weight, Q), (c_norm_weight, C)):
+        if wt is None and not write_cache and n == C:      # a caller that writes no cache norms no latent
+            continue
         _need(wt.dtype == torch.float32 and wt.numel() == n and wt.is_contiguous(), "latent_prep: norm weights float32")
     if n_rot:
         _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
@@ -1044,7 +1047,7 @@ def latent_attention_mma_supports(H, C, R, dtype) -> bool:
     return dtype == torch.bfloat16 and (C + R) % 16 == 0 and 0 < C + R <= 256 and 0 < H <= 64
 
 
-def latent_attention_mma(q, out, cache, ctx, H, C, R, scale, sink=None):
+def latent_attention_mma(q, out, cache, ctx, H, C, R, scale, sink=None, window=0):
     """The same attention on the tensor-core kernels of csrc/attention_mma.cu: the cached rows [c | r] are one
     key/value head of C + R dims that all H query heads share, the values are the rows themselves (the first C
     dims of a head's output are its weighted sum of c), and the sink joins the denominator in the kernels' last
@@ -1069,15 +1072,15 @@ def latent_attention_mma(q, out, cache, ctx, H, C, R, scale, sink=None):
         _i32(ctx.kv_len, ctx.n_seqs, "kv_len")
         _check(lib.ab_attention_decode_sink_bf16(
             _p(q), H * D, _p(out), None, None, None, _p(pages), _p(pages), _p(table), table.shape[1], _p(ctx.tok_seq),
-            _p(ctx.kv_len), T, H, 1, D, ctypes.c_float(scale), 0, -(-width // n_chunks), n_chunks, small, None, None,
-            0, 0, 0, _p(sink), _stream()), "latent_attention_decode")
+            _p(ctx.kv_len), T, H, 1, D, ctypes.c_float(scale), int(window or 0), -(-width // n_chunks), n_chunks, small,
+            None, None, 0, 0, 0, _p(sink), _stream()), "latent_attention_decode")
         return out
     _i32(ctx.tok_pos, T, "tok_pos")
     _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
     tile_seq, tile_q0, n_tiles, tpt = _prefill_tiles(ctx, H, q.device)
     _check(lib.ab_attention_prefill_sink_bf16(
         _p(q), H * D, _p(out), _p(pages), _p(pages), _p(table), table.shape[1], _p(ctx.tok_pos), _p(ctx.cu_q),
-        _p(tile_seq), _p(tile_q0), n_tiles, tpt, H, 1, D, ctypes.c_float(scale), 0, _p(sink), _stream()),
+        _p(tile_seq), _p(tile_q0), n_tiles, tpt, H, 1, D, ctypes.c_float(scale), int(window or 0), _p(sink), _stream()),
         "latent_attention_prefill")
     return out
 
@@ -1097,7 +1100,7 @@ def heads_mm_library(a, a_head_stride, K, w, out, out_head_stride, n_tokens):
     return out
 
 
-def latent_attention(q, out, cache, ctx, H, C, R, scale, sink=None):
+def latent_attention(q, out, cache, ctx, H, C, R, scale, sink=None, window=0):
     """Attention of every token over its sequence's cached latent rows [c | r] (see csrc/latent_attention.cu).
     q float32 [T, H*(C+R)] (keys' up-projection folded in), out float32 [T, H*C], sink float32 [H] or None."""
     pages, table = cache.k, cache.block_table
@@ -1116,20 +1119,33 @@ def latent_attention(q, out, cache, ctx, H, C, R, scale, sink=None):
     _need(C + R <= 1024, f"latent_attention: rows of {C + R} dims are outside 1..1024")
     _i32(ctx.tok_pos, T, "tok_pos")
     _i32(ctx.tok_seq, T, "tok_seq")
-    _check(_lib("latent_attention").ab_latent_attention_simt(
+    _check(_lib("latent_attention").ab_latent_attention_simt_window(
         _p(q), _p(out), _p(pages), _dt(pages), _p(table), table.shape[1], _p(ctx.tok_pos), _p(ctx.tok_seq), _p(sink),
-        T, H, C, R, page, ctypes.c_float(scale), _stream()), "latent_attention")
+        T, H, C, R, page, ctypes.c_float(scale), int(window or 0), _stream()), "latent_attention")
     return out
 
 
 MOE_ACTIVATIONS = {"gelu": 0, "silu": 1}
 
 
-def moe_route(h, router, n_tokens, groups, keep, top, scale, bias=None):
+MOE_SCORES = {"softmax": None, "logit": 0, "sigmoid": 1}
+
+
+def moe_route(h, router, n_tokens, groups, keep, top, scale, bias=None, score="softmax", correction=None, group_top=1,
+              renorm=True):
     """(experts int32 [T, top], weights float32 [T, top]) of every token: softmax over all experts, the `keep`
     best of `groups` groups of neighbours, the `top` best experts of those, weights renormalised times `scale`.
-    `bias` float32 [E] is added to the logits.  (One group, scale 1: the softmax over the chosen logits alone.)"""
-    _cuda(h, router, bias)
+    `bias` float32 [E] is added to the logits.  (One group, scale 1: the softmax over the chosen logits alone.)
+    `score` "sigmoid" (or "logit"): the scores are sigmoid(z) (or z); the choice is made by score + `correction`
+    (float32 [E], if given), a group's score is the sum of its `group_top` largest choice scores, and the weights are
+    the chosen experts' scores without the correction, divided by their sum only if `renorm`."""
+    _cuda(h, router, bias, correction)
+    _need(score in MOE_SCORES, f"moe_route: score must be one of {tuple(MOE_SCORES)}")
+    _need(score != "softmax" or (correction is None and group_top == 1 and renorm),
+          "moe_route: the softmax router has no correction, takes a group's largest score and renormalises")
+    if correction is not None:
+        _need(correction.dtype == torch.float32 and correction.is_contiguous() and correction.numel() == router.shape[0],
+              "moe_route: correction float32 [experts]")
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == router.shape[0],
               "moe_route: bias float32 [experts]")
@@ -1141,6 +1157,13 @@ def moe_route(h, router, n_tokens, groups, keep, top, scale, bias=None):
     idx = torch.empty((max(n_tokens, 1), top), dtype=torch.int32, device=h.device)
     wts = torch.empty((max(n_tokens, 1), top), dtype=torch.float32, device=h.device)
     z = torch.empty((max(n_tokens, 1), E), dtype=torch.float32, device=h.device)
+    if score != "softmax":
+        _need(group_top >= 1 and E // groups <= 128, "moe_route: groups of up to 128 experts, group_top >= 1")
+        _check(_lib("moe").ab_moe_route_scores(
+            _p(h), _dt(h), width, _p(router), _p(bias), _p(correction), n_tokens, width, E, groups, keep, int(group_top),
+            top, MOE_SCORES[score], 1 if renorm else 0, ctypes.c_float(scale), _p(z), _p(idx), _p(wts), _stream()),
+            "moe_route", kernels=2)
+        return idx, wts
     _check(_lib("moe").ab_moe_route_bias(_p(h), _dt(h), width, _p(router), _p(bias), n_tokens, width, E, groups, keep,
                                          top, ctypes.c_float(scale), _p(z), _p(idx), _p(wts), _stream()),
            "moe_route", kernels=2)
@@ -1685,4 +1708,238 @@ def post_norm_add(residual, a, weight, eps, ctx=None, b=None, wa=None, wb=None, 
     _check(_lib("stream_ops").ab_post_norm_add(
         _p(residual), _p(a), _p(b), _dt(a), _p(wa), _p(wb), _p(weight), _p(next_weight), _p(out),
         _dt(out) if out is not None else 0, _p(tok_seq), T, E, ctypes.c_float(eps), _stream()), "post_norm_add")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# layer norm with weight and bias, an embedding with a factor and a table of token pairs, a gate per head, and
+# recurrent mixers whose decay depends on the token (gated linear attention, the gated delta rule)
+
+def layer_norm(residual, delta, weight, bias, eps, out, rows=None, n_rows=None):
+    """Fused residual add and layer norm: residual += delta (when `rows` is None and delta is given);
+    out[i] = (r - mean(r)) / sqrt(var(r) + eps) * weight + bias of row i (or row rows[i]) in out's dtype.
+    residual float32 [T, E]; weight, bias float32 [E]; out None: the addition alone."""
+    _cuda(residual, delta, weight, bias, out, rows)
+    E = residual.shape[-1]
+    T = residual.numel() // E
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "residual must be contiguous float32")
+    for w in (weight, bias):
+        _need(w.dtype == torch.float32 and w.numel() == E and w.is_contiguous(), "layer_norm: weight and bias float32 [E]")
+    if delta is not None:
+        _need(delta.is_contiguous() and delta.numel() == residual.numel(), "delta must match the residual")
+    if rows is not None:
+        n = rows.numel() if n_rows is None else n_rows
+        _i32(rows, n, "rows")
+    else:
+        n = T if n_rows is None else n_rows
+        _need(n <= T, "layer_norm: more rows than the residual has")
+    _need(out is not None or delta is not None, "layer_norm needs delta or out")
+    _need(E * 4 <= 200 * 1024, f"layer_norm: rows of {E} numbers do not fit shared memory")
+    if out is not None:
+        _need(out.is_contiguous() and out.numel() >= n * E, "layer_norm: out too small")
+    _check(_lib("layer_norm").ab_layer_norm(
+        _p(residual), _p(delta), _dt(delta) if delta is not None else 0, _p(rows), _p(weight), _p(bias), _p(out),
+        _dt(out) if out is not None else 0, n, E, ctypes.c_float(eps), _stream()), "layer_norm")
+    return out
+
+
+def post_layer_norm_add(residual, a, weight, bias, eps, mult=1.0, ctx=None, b=None, ca=1.0, cb=1.0, next_weight=None,
+                        next_bias=None, out=None, n_rows=None):
+    """residual[t] += mult * LN(y[t]) with y = ca * a, or ca * a + cb * b for two sub-layers side by side, and LN the
+    layer norm with `weight` and `bias`; then, if `out` is given, out[t] = LN_next(residual[t]) in out's dtype.
+    a, b [T, E] float32 or bfloat16; weights and biases float32 [E]; 32-bit arithmetic."""
+    _cuda(residual, a, b, weight, bias, next_weight, next_bias, out)
+    E = residual.shape[-1]
+    T = (ctx.n_tokens if ctx is not None else residual.numel() // E) if n_rows is None else n_rows
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and residual.numel() >= T * E,
+          "post_layer_norm_add: residual float32 [T, E]")
+    for t in (a, b):
+        if t is not None:
+            _need(t.is_contiguous() and t.shape[-1] == E and t.numel() >= T * E and t.dtype == a.dtype,
+                  "post_layer_norm_add: a and b [T, E] of one dtype")
+    for w in (weight, bias, next_weight, next_bias):
+        if w is not None:
+            _need(w.dtype == torch.float32 and w.is_contiguous() and w.numel() == E,
+                  "post_layer_norm_add: weights and biases float32 [E]")
+    _need(E * 4 <= 200 * 1024, f"post_layer_norm_add: rows of {E} numbers do not fit shared memory")
+    if out is not None:
+        _need(next_weight is not None and next_bias is not None and out.is_contiguous() and out.shape[-1] == E
+              and out.numel() >= T * E, "post_layer_norm_add: out [T, E] comes with the next norm's weight and bias")
+    tok_seq = ctx.tok_seq if ctx is not None else None
+    if tok_seq is not None:
+        _i32(tok_seq, T, "tok_seq")
+    _check(_lib("layer_norm").ab_post_layer_norm_add(
+        _p(residual), _p(a), _p(b), _dt(a), ctypes.c_float(ca), ctypes.c_float(cb), _p(weight), _p(bias),
+        ctypes.c_float(mult), _p(next_weight), _p(next_bias), _p(out), _dt(out) if out is not None else 0, _p(tok_seq),
+        T, E, ctypes.c_float(eps), _stream()), "post_layer_norm_add")
+    return out
+
+
+def embed_pairs(table, scale, out, ctx, pairs=None, buckets=0, mul_prev=0, mul_cur=0, last_token=None):
+    """out[t] = table[token_t] * scale (+ pairs[(prev_t * mul_prev + token_t * mul_cur) mod buckets], row `buckets` for
+    a sequence's first token) as float32.  `last_token` int32 [slots, 1]: each sequence's last token so far, read for
+    the step's first token of a sequence and set to its last."""
+    _cuda(table, pairs, out, last_token)
+    T, E = ctx.n_tokens, table.shape[1]
+    _need(table.dim() == 2 and table.is_contiguous(), "embedding table must be contiguous [V, E]")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[-1] == E and out.numel() >= T * E,
+          "embed_pairs: out float32 [T, E]")
+    _i32(ctx.tokens, T, "tokens")
+    _i32(ctx.tok_seq, T, "tok_seq")
+    if pairs is not None:
+        _need(pairs.dtype == table.dtype and pairs.is_contiguous() and tuple(pairs.shape) == (buckets + 1, E),
+              "embed_pairs: the pair table holds buckets + 1 rows of the embedding's width and dtype")
+        _need(last_token is not None and last_token.dtype == torch.int32 and last_token.is_contiguous(),
+              "embed_pairs: last_token int32 [slots]")
+        _need(0 <= mul_prev < 2 ** 31 and 0 <= mul_cur < 2 ** 31 and buckets > 0, "embed_pairs: multipliers and buckets")
+        _i32(ctx.tok_pos, T, "tok_pos")
+        _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
+        _i32(ctx.slots, ctx.n_seqs, "slots")
+    _check(_lib("stream_ops").ab_embed_pairs(
+        _p(table), _dt(table), ctypes.c_float(scale), _p(pairs), ctypes.c_longlong(buckets), ctypes.c_longlong(mul_prev),
+        ctypes.c_longlong(mul_cur), _p(ctx.tokens), _p(ctx.tok_seq), _p(ctx.tok_pos), _p(ctx.cu_q), _p(ctx.slots),
+        _p(last_token), _p(out), T, E, _stream()), "embed_pairs")
+    return out
+
+
+def head_gate(y, g, g_stride, n_tokens, H, V):
+    """y[t, h, :] *= sigmoid(g[t * g_stride + h]) in place; y [T, H * V]; g: the gates' logits, one per head, in rows
+    of `g_stride` numbers (a view into a wider product is fine)."""
+    _cuda(y, g)
+    _need(y.is_contiguous() and y.shape[-1] == H * V and y.numel() >= n_tokens * H * V, "head_gate: y [T, H * V]")
+    _need(g_stride >= H and g.numel() >= (n_tokens - 1) * g_stride + H, "head_gate: g rows of g_stride >= H numbers")
+    _check(_lib("stream_ops").ab_head_gate(_p(y), _dt(y), _p(g), _dt(g), int(g_stride), n_tokens, H, V, _stream()),
+           "head_gate")
+    return y
+
+
+RECURRENCE_MAX_DIM = 256         # key dims per head that the walk holds in registers
+RECURRENCE_CTAS = 296            # CTAs a walk aims at (two per processor): fewer value columns per CTA when few
+#                                  (sequence, head) pairs would leave processors idle
+
+
+def _recurrence_cols(n_seqs: int, H: int, V: int) -> int:
+    for cols in (32, 16):
+        if n_seqs * H * -(-V // cols) >= RECURRENCE_CTAS or V <= cols // 2:
+            return cols
+    return 8
+
+
+def _f32_rows(t, n, name):
+    _need(t.dtype == torch.float32 and t.stride(-1) == 1 and t.dim() == 2, f"{name}: float32 rows")
+    return t.stride(0)
+
+
+def gated_recurrence(mode, q, k, v, state, out, ctx, H, Hk, D, V, qscale=1.0, decay=None, beta=None, write_state=True):
+    """One walk of a recurrent mixer over the step's tokens; q, k [T, Hk * D] and v [T, H * V] float32 (views with a
+    row stride are fine), state float32 [slots, H, D, V], out float32 [T, H * V].
+    mode "channel": S <- diag(a_t) S + k_t v_t^T, o_t = S^T (q_t qscale), decay a [T, H * D];
+    mode "delta": S <- g_t S; u = beta_t (v_t - S^T k_t); S <- S + k_t u^T; o_t = S^T (q_t qscale), decay g and beta [T, H]."""
+    _cuda(q, k, v, state, out, decay, beta)
+    T = ctx.n_tokens
+    _need(mode in ("channel", "delta"), "gated_recurrence: mode channel or delta")
+    _need(0 < D <= RECURRENCE_MAX_DIM and H % Hk == 0, f"gated_recurrence: {D} dims per head are outside 1..{RECURRENCE_MAX_DIM}")
+    ldq, ldk, ldv = _f32_rows(q, T, "q"), _f32_rows(k, T, "k"), _f32_rows(v, T, "v")
+    _need(q.shape[0] >= T and k.shape[0] >= T and v.shape[0] >= T and q.shape[1] == Hk * D and k.shape[1] == Hk * D
+          and v.shape[1] == H * V, "gated_recurrence: q, k [T, Hk * D], v [T, H * V]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, D, V),
+          "gated_recurrence: state float32 [slots, H, D, V]")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[-1] == H * V and out.numel() >= T * H * V,
+          "gated_recurrence: out float32 [T, H * V]")
+    if mode == "channel":
+        _need(decay is not None and decay.shape[0] >= T and decay.shape[1] == H * D, "gated_recurrence: decay [T, H * D]")
+        ldd, dsc = _f32_rows(decay, T, "decay"), None
+        dvec = decay
+    else:
+        for t in (decay, beta):
+            _need(t is not None and t.dtype == torch.float32 and t.is_contiguous() and t.shape[-1] == H
+                  and t.numel() >= T * H, "gated_recurrence: decay and beta float32 [T, H]")
+        ldd, dvec, dsc = 0, None, decay
+    _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
+    _i32(ctx.slots, ctx.n_seqs, "slots")
+    cols = _recurrence_cols(ctx.n_seqs, H, V)
+    _check(_lib("gated_recurrence").ab_gated_recurrence(
+        0 if mode == "channel" else 1, _p(q), ldq, _p(k), ldk, _p(v), ldv, _p(dvec), ldd, _p(dsc), _p(beta),
+        ctypes.c_float(qscale), _p(state), _p(out), _p(ctx.cu_q), _p(ctx.slots), ctx.n_seqs, H, Hk, D, V, cols,
+        1 if write_state else 0, _stream()), "gated_recurrence")
+    return out
+
+
+def gla_decay(y, w2, bias, tau, out, n_tokens):
+    """out[t, c] = sigmoid(z)^(1/tau) with z = bias[c] + w2[c] . y[t]; y float32 rows of `rank` numbers (a view with a
+    row stride is fine), w2 float32 [channels, rank], out float32 [T, channels]."""
+    _cuda(y, w2, bias, out)
+    channels, rank = w2.shape
+    ldy = _f32_rows(y, n_tokens, "y")
+    _need(y.shape[1] == rank and y.shape[0] >= n_tokens, "gla_decay: y [T, rank]")
+    _need(w2.dtype == torch.float32 and w2.is_contiguous(), "gla_decay: w2 float32 [channels, rank]")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == channels, "gla_decay: bias float32")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[-1] == channels and out.numel() >= n_tokens * channels,
+          "gla_decay: out float32 [T, channels]")
+    _need(tau > 0 and rank <= 1536, "gla_decay: tau positive, rank up to 1536")
+    _check(_lib("gated_recurrence").ab_gla_decay(_p(y), ldy, _p(w2), _p(bias), ctypes.c_float(tau), _p(out), n_tokens,
+                                                 channels, rank, _stream()), "gla_decay")
+    return out
+
+
+CONV_MAX_TAPS = 17
+
+
+def gdr_prepare(x, taps_w, conv_state, A_log, dt_bias, b_off, a_off, qscale, unit_eps, qkv, beta, decay, ctx, H, G, D, V,
+                write_state=True):
+    """What the gated delta rule's walk reads, from the projected rows x float32 [T, ld] = [q | k | v | ...]: the short
+    causal convolution per channel over time (taps_w float32 [2 G D + H V, taps], last column the token's own) with
+    SiLU; q and k heads as unit vectors, q times qscale; beta = sigmoid(x[b_off + h]); decay = exp(-exp(A_log[h]) *
+    softplus(x[a_off + h] + dt_bias[h])).  conv_state float32 [slots, taps - 1, channels]: a sequence's last inputs,
+    read here and, if `write_state`, moved on by the step's."""
+    _cuda(x, taps_w, conv_state, A_log, dt_bias, qkv, beta, decay)
+    T = ctx.n_tokens
+    Cc = 2 * G * D + H * V
+    taps = taps_w.shape[1]
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2 and x.shape[0] >= T
+          and x.shape[1] >= max(Cc, b_off + H, a_off + H), "gdr_prepare: x float32 [T, ld]")
+    _need(taps_w.dtype == torch.float32 and taps_w.is_contiguous() and taps_w.shape[0] == Cc and 1 <= taps <= CONV_MAX_TAPS,
+          f"gdr_prepare: taps float32 [channels, 1..{CONV_MAX_TAPS}]")
+    _need(conv_state.dtype == torch.float32 and conv_state.is_contiguous()
+          and tuple(conv_state.shape[1:]) == (max(taps - 1, 1), Cc), "gdr_prepare: conv_state float32 [slots, taps - 1, channels]")
+    for t in (A_log, dt_bias):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == H, "gdr_prepare: A_log, dt_bias float32 [H]")
+    _need(qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.shape[-1] == Cc and qkv.numel() >= T * Cc,
+          "gdr_prepare: qkv float32 [T, channels]")
+    for t in (beta, decay):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() >= T * H, "gdr_prepare: beta, decay float32 [T, H]")
+    _need(Cc * 4 <= 200 * 1024, "gdr_prepare: a token's channels do not fit shared memory")
+    _i32(ctx.tok_seq, T, "tok_seq")
+    _i32(ctx.cu_q, ctx.n_seqs + 1, "cu_q")
+    _i32(ctx.slots, ctx.n_seqs, "slots")
+    _check(_lib("gated_recurrence").ab_gdr_prepare(
+        _p(x), x.shape[1], _p(taps_w), taps, _p(conv_state), _p(A_log), _p(dt_bias), int(b_off), int(a_off),
+        ctypes.c_float(qscale), ctypes.c_float(unit_eps), _p(qkv), _p(beta), _p(decay), _p(ctx.tok_seq), _p(ctx.cu_q),
+        _p(ctx.slots), T, ctx.n_seqs, H, G, D, V, 1 if write_state else 0, _stream()), "gdr_prepare",
+        kernels=2 if write_state and taps > 1 else 1)
+
+
+HEAD_GATES = {None: 0, "silu": 1, "sigmoid": 2}
+
+
+def head_norm_gate(o, weight, gate, gate_act, eps, out, ctx, H, V):
+    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * act(gate[t, h, :]) in out's dtype; o float32
+    [T, H * V], weight float32 [V] (one for all heads) or None, gate float32 rows of H * V numbers (a view with a row
+    stride is fine) or None, act "silu" or "sigmoid"."""
+    _cuda(o, weight, gate, out)
+    T = ctx.n_tokens
+    _need(o.dtype == torch.float32 and o.is_contiguous() and o.shape[-1] == H * V and o.numel() >= T * H * V,
+          "head_norm_gate: o float32 [T, H * V]")
+    if weight is not None:
+        _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == V, "head_norm_gate: weight float32 [V]")
+    ldg = 0
+    if gate is not None:
+        ldg = _f32_rows(gate, T, "gate")
+        _need(gate.shape[0] >= T and gate.shape[1] == H * V and gate_act in ("silu", "sigmoid"), "head_norm_gate: gate [T, H * V]")
+    _need(out.is_contiguous() and out.shape[-1] == H * V and out.numel() >= T * H * V, "head_norm_gate: out [T, H * V]")
+    _i32(ctx.tok_seq, T, "tok_seq")
+    _check(_lib("gated_recurrence").ab_head_norm_gate(
+        _p(o), _p(weight), _p(gate), ldg, HEAD_GATES[gate_act if gate is not None else None], _p(out), _dt(out),
+        _p(ctx.tok_seq), T, H, V, ctypes.c_float(eps), _stream()), "head_norm_gate")
     return out

@@ -140,7 +140,8 @@ def load(name: str) -> ctypes.CDLL:
 
 
 ALL_LIBRARIES = ("elementwise", "attention_simt", "attention_mma", "gemm_f32", "gemv_bf16", "gemm_tc", "attention_tc", "attention_stream", "sampling", "safetensors_reader",
-                 "mlstm", "latent_attention", "moe", "linear_attention", "attention_maps", "stream_ops")
+                 "mlstm", "latent_attention", "moe", "linear_attention", "attention_maps", "stream_ops", "layer_norm",
+                 "gated_recurrence")
 
 
 def build_all(names=ALL_LIBRARIES) -> list[Path]:

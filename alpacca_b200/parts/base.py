@@ -109,6 +109,26 @@ class HalfSum:
     eps: float
 
 
+@dataclass
+class WeightedSum:
+    """What two mixers side by side hand to the block where the sub-layer's output is ca * a + cb * b, not formed yet:
+    the block's kernel that adds a sub-layer's output to the stream forms it."""
+    a: torch.Tensor
+    b: torch.Tensor
+    ca: float
+    cb: float
+
+
+def mixer_cache_specs(mixer) -> list:
+    """What a mixer keeps per sequence, as a list: its `cache_specs()` if it keeps several things, else its one
+    `cache_spec()` (or nothing)."""
+    several = getattr(mixer, "cache_specs", None)
+    if several is not None:
+        return [s for s in several() if s is not None]
+    one = mixer.cache_spec()
+    return [one] if one is not None else []
+
+
 class Part:
     """Base of all parts: parameters by checkpoint name, loading, sub-parts."""
 

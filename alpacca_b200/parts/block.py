@@ -15,7 +15,8 @@ from dataclasses import dataclass
 import torch
 
 from .. import ops
-from .base import Block, FeedForward, HalfSum, Mixer, Norm, OwedNorm
+from .base import Block, FeedForward, HalfSum, Mixer, Norm, OwedNorm, WeightedSum
+from .layer_norm import LayerNorm
 
 
 @dataclass
@@ -89,17 +90,25 @@ class SandwichBlock(Block):
     (two mixers side by side whose normed outputs are averaged); the same kernel forms it.  The norms are
     `RMSNorm`s (weight per column, eps), 32-bit arithmetic.  Where the next block is of this kind too, the kernel
     after this block's last sub-layer leaves that block's first norm as well (`first_plain_norm`,
-    `HiddenStream.ready`)."""
+    `HiddenStream.ready`).
+
+    With `LayerNorm`s (weight and bias, centred) the same arrangement runs `ops.post_layer_norm_add`; then
+    `residual_mult` m scales what joins the stream, x += m * Post(Sublayer(Norm(x))), and two mixers side by side
+    may hand over a `WeightedSum` (c_left * left + c_right * right)."""
 
     def __init__(self, norm1: Norm, mixer: Mixer, post1: Norm, norm2: Norm | None = None,
-                 ffn: FeedForward | None = None, post2: Norm | None = None):
+                 ffn: FeedForward | None = None, post2: Norm | None = None, residual_mult: float = 1.0):
         if (ffn is None) != (norm2 is None) or (ffn is None) != (post2 is None):
             raise ValueError("a feed-forward comes with a norm before and a norm after it")
+        self.residual_mult = float(residual_mult)
+        if self.residual_mult != 1.0 and not all(isinstance(n, LayerNorm) for n in (post1, post2) if n is not None):
+            raise ValueError("a factor on what joins the stream comes with layer norms after the sub-layers "
+                             "(an RMS norm takes it into its weight: `RMSNorm(scale=)`)")
         self.norm1, self.mixer, self.post1 = norm1, mixer, post1
         self.norm2, self.ffn, self.post2 = norm2, ffn, post2
 
     def cache_specs(self) -> list:
-        several = getattr(self.mixer, "cache_specs", None)      # mixers side by side: an entry for each
+        several = getattr(self.mixer, "cache_specs", None)      # mixers side by side, a mixer with two states: an entry for each
         if several is not None:
             return several()
         return super().cache_specs()
@@ -119,21 +128,36 @@ class SandwichBlock(Block):
         stream.delta = None
         y = self.mixer.forward(h, ctx, cache, write_cache)
         last = self.post1 if self.ffn is None else self.post2
-        if after is not None and not (hasattr(after, "weight") and getattr(after, "eps", None) == last.eps):
+        if after is not None and not (hasattr(after, "weight") and getattr(after, "eps", None) == last.eps
+                                      and isinstance(after, LayerNorm) == isinstance(last, LayerNorm)):
             after = None
         if self.ffn is not None:
-            h = _post_add(self.post1, stream.residual, y, ctx, then=self.norm2)
+            h = _post_add(self.post1, stream.residual, y, ctx, then=self.norm2, mult=self.residual_mult)
             y = self.ffn.forward(h, ctx)
-        rows = _post_add(last, stream.residual, y, ctx, then=after)
+        rows = _post_add(last, stream.residual, y, ctx, then=after, mult=self.residual_mult)
         if after is not None:
             stream.ready = (after, rows)
 
 
-def _post_add(post: Norm, residual, y, ctx, then: Norm | None = None):
-    """residual += post(y); returns then(residual) in the activation dtype where `then` is given."""
+def _post_add(post: Norm, residual, y, ctx, then: Norm | None = None, mult: float = 1.0):
+    """residual += mult * post(y); returns then(residual) in the activation dtype where `then` is given."""
     out = None
     if then is not None:
         out = torch.empty((residual.shape[0], residual.shape[-1]), dtype=then.opts.dtype, device=residual.device)
+    if isinstance(post, LayerNorm):
+        if then is not None and (not isinstance(then, LayerNorm) or then.eps != post.eps):
+            raise ValueError("the norm after a sub-layer and the norm that reads the stream next are of one kind and eps")
+        more = {}
+        if isinstance(y, WeightedSum):
+            more = {"b": y.b, "ca": y.ca, "cb": y.cb}
+            y = y.a
+        elif isinstance(y, HalfSum):
+            raise ValueError("a half sum of normed outputs is formed before an RMS norm, not before a layer norm")
+        return ops.post_layer_norm_add(residual, y, post.weight, post.bias, post.eps, mult, ctx,
+                                       next_weight=then.weight if then else None,
+                                       next_bias=then.bias if then else None, out=out, **more)
+    if isinstance(y, WeightedSum) or mult != 1.0:
+        raise ValueError("a weighted sum of two mixers and a factor on the stream's addition come with layer norms")
     more = {}
     if isinstance(y, HalfSum):
         more = {"b": y.b, "wa": y.wa, "wb": y.wb}

@@ -26,6 +26,8 @@ Options, each a constructor argument:
                      attention over that whole row is computed once, and o_h = sum_g T[h, g] A[g, group of h]; the
                      rows of W_q are reordered at load so that neighbouring query vectors read different key heads.
     gate             the concatenated heads are multiplied by sigmoid(W_g h) (tensor `<prefix>.<gate>`) before W_o
+    head_gate        every head's output is multiplied by sigmoid(W_g h)_h, ONE number per head and token (tensor
+                     `<prefix>.<head_gate>` [H, width]), before W_o; its rows ride in the projections' product
 
 The rotation turns the first n_rot dims of every query and key vector (each map by itself).  In bfloat16 with key
 and value sizes in steps of 16, prompts and decode steps run on the tensor-core kernels of csrc/attention_mma.cu
@@ -50,7 +52,8 @@ class MapsAttention(Mixer):
                  n_maps: int = 1, bias: bool = False, qk_norm: bool = False, values_are_keys: bool = False,
                  sink: bool = False, difference: float | None = None, names=("q", "k", "v", "o"),
                  weight_suffix: str = "", bias_suffix: str = ".b", out_dtype=None, qk_norm_weight: bool = True,
-                 value_norm: bool = False, head_mix: str | None = None, gate: str | None = None):
+                 value_norm: bool = False, head_mix: str | None = None, gate: str | None = None,
+                 head_gate: str | None = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{prefix}: {n_heads} heads cannot share {n_kv_heads} key/value heads")
         self.opts, self.prefix = opts, prefix
@@ -67,6 +70,9 @@ class MapsAttention(Mixer):
         if not (0 < self.Dk <= big and 0 < self.Dv <= big):
             raise ValueError(f"{prefix}: head sizes {self.Dk} and {self.Dv} are outside 1..{big}")
         self.qk_norm_weight, self.value_norm, self.head_mix, self.gate = bool(qk_norm_weight), bool(value_norm), head_mix, gate
+        self.head_gate = head_gate
+        if head_gate is not None and (gate is not None or head_mix is not None):
+            raise ValueError(f"{prefix}: a gate per head stands alone (no gate per value, no mixed heads)")
         if gate is not None and head_mix is None:
             raise ValueError(f"{prefix}: the output gate is applied by the kernel that mixes the heads (head_mix)")
         if head_mix is not None:
@@ -89,6 +95,9 @@ class MapsAttention(Mixer):
         if gate is not None:
             self.gate_offset = sum(r for _, r in sources)
             sources.append((f"{prefix}.{gate}", self.H * self.Dv))
+        if head_gate is not None:
+            self.gate_offset = sum(r for _, r in sources)
+            sources.append((f"{prefix}.{head_gate}", self.H))
         self.qkv = Linear(opts, width, sources, bias=bias, weight_suffix=weight_suffix, bias_suffix=bias_suffix)
         self.out = Linear(opts, self.H * self.Dv, [(f"{prefix}.{o}", width)], weight_suffix=weight_suffix,
                           out_dtype=out_dtype)
@@ -169,5 +178,7 @@ class MapsAttention(Mixer):
         attend(buf, buf.shape[-1], att, cache, ctx, self.H, self.G, self.M, self.Dk, self.Dv, self.scale,
                self.window or 0, self.sink, coef=self.coef, unit_norm=unit, eps=self.eps,
                out_scale=(1.0 - self.difference) if unit else 1.0)
+        if self.head_gate is not None:
+            ops.head_gate(att, buf.reshape(-1)[self.gate_offset:], buf.shape[-1], T, self.H, self.Dv)
         # after a kernel that fills the processors' shared memory the product starts when that kernel has ended
         return self.out.forward(att, n_rows=T, start_early=False, then=then)
