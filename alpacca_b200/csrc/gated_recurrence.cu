@@ -8,8 +8,11 @@
 //       per head and token; the read-out sees the token's own write
 //
 // The walk (`recurrence_kernel`): a CTA per (sequence, head, tile of value columns); a column's D entries are spread
-// over four neighbouring lanes' registers (rows r, r + 4, ..), q, k and the decays of eight tokens at a time wait in
-// shared memory, a column's dot products are summed over its four lanes by shuffles.  The order of additions depends
+// over 8, 16 or 32 neighbouring lanes' registers (a part of the rows each, read 16 bytes at a time), q, k and the decays of eight tokens at a time arrive in
+// shared memory by `cp.async` through a ring of four buffers (three rounds' rows are on their way while one is walked), a
+// column's dot products run in four chains per lane; the lanes' shares of a read-out wait in shared memory and are
+// added after the round, so that the walk of a decay per channel has no exchange between lanes and no barrier in
+// it (the delta rule needs one exchange per token, S^T k over all rows, by shuffles).  The order of additions depends
 // on the column alone, so a token's output is bitwise the same in a prompt, a portion or a step of one token.
 //
 // Around it: `gla_decay` (a = sigmoid(z)^(1/tau) with z = W_2 y + b from the low-rank projection's first half y),
@@ -21,107 +24,232 @@
 #include "launch.cuh"
 
 #define REC_TOKENS 8        // tokens staged per round of the walk
+#define REC_STAGES 4        // rounds whose rows are in flight or in use: the walk of a round is short against the memory's latency
 #define CONV_MAX_TAPS 16
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 
-template <int DR, int MODE>
+// 4 or 16 bytes from global to shared memory without passing registers; the copies of a round are one group
+__device__ __forceinline__ void copy_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void copy_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+
+// Who copies what in a round: thread `tid` copies piece `c` (4 floats with 16-byte copies, else 1) of the rows of
+// tokens tt = t_first, t_first + t_step, ..; worked out once, so that a round's copies cost no division.
+struct RowCopier {
+  int c, t_first, t_step;      // c < 0: this thread copies nothing
+  __device__ __forceinline__ RowCopier(int pieces, int tid, int n_threads) {
+    if (pieces <= 0) { c = -1; t_first = t_step = 1; return; }
+    if (n_threads >= pieces) {
+      t_step = n_threads / pieces;
+      c = tid < t_step * pieces ? tid % pieces : -1;
+      t_first = tid / pieces;
+    } else {                     // more pieces than threads: every thread takes several of every row
+      t_step = 1;
+      t_first = 0;
+      c = tid;
+    }
+  }
+};
+
+// rows of `n` tokens, `len` floats each, from `src + t * ld` to `dst + tt * pitch`.  With PART > 4 a row is laid out
+// in parts of that many floats, each followed by four unused ones (element d at (d / PART) * (PART + 4) + d % PART),
+// so that the lanes of a column, which each read their own part 16 bytes at a time, meet different banks.
+template <int PART>
+__device__ __forceinline__ void stage_rows(const RowCopier& w, float* dst, int pitch, const float* src, size_t ld, int n,
+                                           int len, bool vec) {
+  if (w.c < 0) return;
+  const int pieces = vec ? len >> 2 : len;
+  for (int c = w.c; c < pieces; c += blockDim.x) {
+    const int d = vec ? c << 2 : c;
+    const int at = PART > 4 ? (d / PART) * (PART + 4) + d % PART : d;
+    for (int tt = w.t_first; tt < n; tt += w.t_step) {
+      if (vec) copy_async16(dst + tt * pitch + at, src + (size_t)tt * ld + d);
+      else copy_async4(dst + tt * pitch + at, src + (size_t)tt * ld + d);
+    }
+  }
+}
+
+// One token of one thread: its DR rows of column j.  The thread's share of the read-out goes to `share` (shared
+// memory); the shares of a column's lanes are added after the round, so that a decay per channel needs no exchange
+// between lanes while the tokens are walked.  The delta rule needs one per token: S^T k over all rows.
+template <int DR, int LANES, int MODE>
+__device__ __forceinline__ void walk_token(float (&S)[DR], const float4* __restrict__ qr, const float4* __restrict__ kr,
+                                           const float4* __restrict__ ar, float vj, float g, float bt, float* share) {
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;      // four chains, added in a fixed order
+  if (MODE == 0) {
+#pragma unroll
+    for (int i = 0; i < DR; i += 4) {
+      const float4 a = ar[i >> 2], kk = kr[i >> 2], qq = qr[i >> 2];
+      S[i] = a.x * S[i] + kk.x * vj;
+      S[i + 1] = a.y * S[i + 1] + kk.y * vj;
+      S[i + 2] = a.z * S[i + 2] + kk.z * vj;
+      S[i + 3] = a.w * S[i + 3] + kk.w * vj;
+      a0 += S[i] * qq.x;
+      a1 += S[i + 1] * qq.y;
+      a2 += S[i + 2] * qq.z;
+      a3 += S[i + 3] * qq.w;
+    }
+  } else {
+    float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < DR; i += 4) {
+      const float4 kk = kr[i >> 2];
+      S[i] *= g;
+      S[i + 1] *= g;
+      S[i + 2] *= g;
+      S[i + 3] *= g;
+      d0 += S[i] * kk.x;
+      d1 += S[i + 1] * kk.y;
+      d2 += S[i + 2] * kk.z;
+      d3 += S[i + 3] * kk.w;
+    }
+    float dot = (d0 + d1) + (d2 + d3);
+#pragma unroll
+    for (int o = 1; o < LANES; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float u = bt * (vj - dot);
+#pragma unroll
+    for (int i = 0; i < DR; i += 4) {
+      const float4 kk = kr[i >> 2], qq = qr[i >> 2];
+      S[i] += kk.x * u;
+      S[i + 1] += kk.y * u;
+      S[i + 2] += kk.z * u;
+      S[i + 3] += kk.w * u;
+      a0 += S[i] * qq.x;
+      a1 += S[i + 1] * qq.y;
+      a2 += S[i + 2] * qq.z;
+      a3 += S[i + 3] * qq.w;
+    }
+  }
+  *share = (a0 + a1) + (a2 + a3);
+}
+
+template <int DR, int LANES, int MODE>
 __global__ void recurrence_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
                                   const float* __restrict__ v, int ldv, const float* __restrict__ dvec, int ldd,
                                   const float* __restrict__ dsc, const float* __restrict__ beta, float qscale,
                                   float* __restrict__ state, float* __restrict__ out, const int* __restrict__ cu_q,
-                                  const int* __restrict__ slots, int H, int Hk, int D, int V, int CV, int write_state) {
-  extern __shared__ float rec_sm[];
-  constexpr int D4 = DR * 4;
+                                  const int* __restrict__ slots, int H, int Hk, int D, int V, int CV, int write_state,
+                                  int vec) {
+  extern __shared__ __align__(16) float rec_sm[];
+  constexpr int DRP = DR > 4 ? DR + 4 : DR;     // a lane's part of a row, and the gap behind it
+  constexpr int P4 = LANES * DRP;              // a token's row of q, k or decays
   pdl_wait();
   pdl_trigger();
   const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * CV;
   const int slot = slots[b];
   if (slot < 0) return;
   const int kh = h / (H / Hk);
-  const int tid = threadIdx.x, col = tid >> 2, r = tid & 3;
-  const int j = col0 + col;
-  float* qs = rec_sm;                          // [REC_TOKENS][D4]
-  float* ks = qs + REC_TOKENS * D4;            // [REC_TOKENS][D4]
-  float* as = ks + REC_TOKENS * D4;            // [REC_TOKENS][D4]   (mode 0)
-  float* vs = as + (MODE == 0 ? REC_TOKENS * D4 : 0);      // [REC_TOKENS][CV]
-  float* os = vs + REC_TOKENS * CV;            // [REC_TOKENS][CV]
-  float* sc = os + REC_TOKENS * CV;            // [REC_TOKENS][2]    (mode 1: g, beta)
-  float S[DR];
+  const int tid = threadIdx.x, col = tid / LANES, r = tid % LANES;
+  // a ring of buffers of a round's tokens: q, k (and the decays) of P4 floats each, CV values, two numbers per token
+  constexpr int NV = MODE == 0 ? 3 : 2;
+  const int per_buf = REC_TOKENS * (NV * P4 + CV + 4);
+  float* shares = rec_sm + REC_STAGES * per_buf;      // [REC_TOKENS][CV][LANES]: the lanes' shares of a round's read-outs
+  float S[DR];                                 // rows r * DR .. r * DR + DR - 1 of column j
   float* st = state + ((size_t)slot * H + h) * D * V;
+  // The tile of the state comes through shared memory: neighbouring threads fetch neighbouring columns of a row
+  // (whole 32-byte pieces of memory), then every thread picks its rows.
+  for (int idx = tid; idx < D * CV; idx += blockDim.x) {
+    const int d = idx / CV, c = idx - d * CV;
+    rec_sm[idx] = col0 + c < V ? st[(size_t)d * V + col0 + c] : 0.f;
+  }
+  __syncthreads();
 #pragma unroll
   for (int i = 0; i < DR; ++i) {
-    const int d = r + 4 * i;
-    S[i] = (d < D && j < V) ? st[(size_t)d * V + j] : 0.f;
+    const int d = r * DR + i;
+    S[i] = d < D ? rec_sm[d * CV + col] : 0.f;
   }
+  __syncthreads();
+  if (LANES * DR != D)                         // rows behind D are read as zeros
+    for (int idx = tid; idx < REC_STAGES * per_buf; idx += blockDim.x) rec_sm[idx] = 0.f;
   const int t0 = cu_q[b], t1 = cu_q[b + 1];
-  for (int c0 = t0; c0 < t1; c0 += REC_TOKENS) {
+  const int cw = min(CV, V - col0);                        // this tile's columns
+  const bool vec_v = vec && (cw & 3) == 0 && (col0 & 3) == 0;
+  const RowCopier rows(vec ? D >> 2 : D, tid, blockDim.x), vals(vec_v ? cw >> 2 : cw, tid, blockDim.x);
+  __syncthreads();
+  auto stage = [&](int buf, int c0) {
     const int n = min(REC_TOKENS, t1 - c0);
-    __syncthreads();
-    for (int idx = tid; idx < n * D4; idx += blockDim.x) {
-      const int tt = idx / D4, d = idx - tt * D4;
-      const size_t t = (size_t)(c0 + tt);
-      const bool in = d < D;
-      qs[idx] = in ? q[t * ldq + (size_t)kh * D + d] * qscale : 0.f;
-      ks[idx] = in ? k[t * ldk + (size_t)kh * D + d] : 0.f;
-      if (MODE == 0) as[idx] = in ? dvec[t * ldd + (size_t)h * D + d] : 0.f;
+    float* base = rec_sm + buf * per_buf;
+    stage_rows<DR>(rows, base, P4, q + (size_t)c0 * ldq + (size_t)kh * D, ldq, n, D, vec);
+    stage_rows<DR>(rows, base + REC_TOKENS * P4, P4, k + (size_t)c0 * ldk + (size_t)kh * D, ldk, n, D, vec);
+    if (MODE == 0)
+      stage_rows<DR>(rows, base + 2 * REC_TOKENS * P4, P4, dvec + (size_t)c0 * ldd + (size_t)h * D, ldd, n, D, vec);
+    float* vs = base + NV * REC_TOKENS * P4;
+    stage_rows<0>(vals, vs, CV, v + (size_t)c0 * ldv + (size_t)h * V + col0, ldv, n, cw, vec_v);
+    if (MODE == 1 && tid < n) {
+      float* sc = vs + REC_TOKENS * CV;
+      copy_async4(sc + 2 * tid, dsc + (size_t)(c0 + tid) * H + h);
+      copy_async4(sc + 2 * tid + 1, beta + (size_t)(c0 + tid) * H + h);
     }
+    copy_commit();
+  };
+  // REC_STAGES - 1 rounds are asked for before the first is walked; every turn of the loop commits one group (an
+  // empty one once the tokens have run out), so that "all but the newest REC_STAGES - 1" is always this round's
+#pragma unroll
+  for (int i = 0; i < REC_STAGES - 1; ++i) {
+    if (t0 + i * REC_TOKENS < t1) stage(i, t0 + i * REC_TOKENS);
+    else copy_commit();
+  }
+  int buf = 0;
+  for (int c0 = t0; c0 < t1; c0 += REC_TOKENS, buf = (buf + 1) % REC_STAGES) {
+    const int n = min(REC_TOKENS, t1 - c0);
+    const int ahead = c0 + (REC_STAGES - 1) * REC_TOKENS;
+    if (ahead < t1) stage((buf + REC_STAGES - 1) % REC_STAGES, ahead);     // into the buffer that the round before left
+    else copy_commit();
+    copy_wait<REC_STAGES - 1>();
+    __syncthreads();
+    const float* qs = rec_sm + buf * per_buf + r * DRP;
+    const float* ks = qs + REC_TOKENS * P4;
+    const float* as = ks + REC_TOKENS * P4;
+    const float* vs = rec_sm + buf * per_buf + NV * REC_TOKENS * P4;
+    const float* sc = vs + REC_TOKENS * CV;
+    float* mine = shares + col * LANES + r;
+    if (n == REC_TOKENS) {
+#pragma unroll
+      for (int tt = 0; tt < REC_TOKENS; ++tt)
+        walk_token<DR, LANES, MODE>(S, reinterpret_cast<const float4*>(qs + tt * P4), reinterpret_cast<const float4*>(ks + tt * P4),
+                                    reinterpret_cast<const float4*>(as + tt * P4), vs[tt * CV + col],
+                                    MODE == 1 ? sc[2 * tt] : 0.f, MODE == 1 ? sc[2 * tt + 1] : 0.f, mine + tt * CV * LANES);
+    } else {
+      for (int tt = 0; tt < n; ++tt)
+        walk_token<DR, LANES, MODE>(S, reinterpret_cast<const float4*>(qs + tt * P4), reinterpret_cast<const float4*>(ks + tt * P4),
+                                    reinterpret_cast<const float4*>(as + tt * P4), vs[tt * CV + col],
+                                    MODE == 1 ? sc[2 * tt] : 0.f, MODE == 1 ? sc[2 * tt + 1] : 0.f, mine + tt * CV * LANES);
+    }
+    __syncthreads();
+    // a column's read-out: its lanes' shares, added in lane order
     for (int idx = tid; idx < n * CV; idx += blockDim.x) {
       const int tt = idx / CV, c = idx - tt * CV;
-      vs[idx] = col0 + c < V ? v[(size_t)(c0 + tt) * ldv + (size_t)h * V + col0 + c] : 0.f;
-    }
-    if (MODE == 1)
-      for (int idx = tid; idx < n; idx += blockDim.x) {
-        sc[2 * idx] = dsc[(size_t)(c0 + idx) * H + h];
-        sc[2 * idx + 1] = beta[(size_t)(c0 + idx) * H + h];
-      }
-    __syncthreads();
-    for (int tt = 0; tt < n; ++tt) {
-      const float vj = vs[tt * CV + col];
-      const float* qr = qs + tt * D4 + r;
-      const float* kr = ks + tt * D4 + r;
+      if (col0 + c >= V) continue;
+      const float4* sh = reinterpret_cast<const float4*>(shares + (size_t)idx * LANES);
       float acc = 0.f;
-      if (MODE == 0) {
-        const float* ar = as + tt * D4 + r;
 #pragma unroll
-        for (int i = 0; i < DR; ++i) {
-          S[i] = ar[4 * i] * S[i] + kr[4 * i] * vj;
-          acc += S[i] * qr[4 * i];
-        }
-      } else {
-        const float g = sc[2 * tt], bt = sc[2 * tt + 1];
-        float dot = 0.f;
-#pragma unroll
-        for (int i = 0; i < DR; ++i) {
-          S[i] *= g;
-          dot += S[i] * kr[4 * i];
-        }
-        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-        const float u = bt * (vj - dot);
-#pragma unroll
-        for (int i = 0; i < DR; ++i) {
-          S[i] += kr[4 * i] * u;
-          acc += S[i] * qr[4 * i];
-        }
+      for (int i = 0; i < LANES / 4; ++i) {
+        const float4 p = sh[i];
+        acc += (p.x + p.y) + (p.z + p.w);
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      if (r == 0) os[tt * CV + col] = acc;
-    }
-    __syncthreads();
-    for (int idx = tid; idx < n * CV; idx += blockDim.x) {
-      const int tt = idx / CV, c = idx - tt * CV;
-      if (col0 + c < V) out[(size_t)(c0 + tt) * H * V + (size_t)h * V + col0 + c] = os[idx];
+      out[(size_t)(c0 + tt) * H * V + (size_t)h * V + col0 + c] = acc * qscale;
     }
   }
   if (!write_state) return;
+  __syncthreads();                             // (every copy into the ring has landed: the last rounds asked for none)
 #pragma unroll
   for (int i = 0; i < DR; ++i) {
-    const int d = r + 4 * i;
-    if (d < D && j < V) st[(size_t)d * V + j] = S[i];
+    const int d = r * DR + i;
+    if (d < D) rec_sm[d * CV + col] = S[i];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < D * CV; idx += blockDim.x) {
+    const int d = idx / CV, c = idx - d * CV;
+    if (col0 + c < V) st[(size_t)d * V + col0 + c] = rec_sm[idx];
   }
 }
 
@@ -136,25 +264,43 @@ AB_API int ab_gated_recurrence(int mode, const float* q, int ldq, const float* k
   if (H <= 0 || Hk <= 0 || H % Hk || D <= 0 || D > 256 || V <= 0 || (cols != 8 && cols != 16 && cols != 32)) return AB_BAD_ARG;
   if (!q || !k || !v || !state || !out || !cu_q || !slots) return AB_BAD_ARG;
   if (mode == 0 ? !dvec : (mode != 1 || !dsc || !beta)) return AB_BAD_ARG;
-  const int DR = D <= 32 ? 8 : (D <= 64 ? 16 : (D <= 128 ? 32 : 64));
-  const int D4 = DR * 4;
-  const size_t smem = sizeof(float) * ((size_t)REC_TOKENS * D4 * (mode == 0 ? 3 : 2) + 2 * REC_TOKENS * cols + 2 * REC_TOKENS);
+  // More lanes per column where few (sequence, head, column) triples would leave the schedulers with a warp or none
+  // each: a walk is a chain of dependent steps per token, and what hides its latency is other warps.
+  int lanes = 8;
+  const long long threads8 = (long long)n_seqs * H * ((V + cols - 1) / cols) * cols * 8;
+  if (mode == 0 && D > 32 && threads8 < 600LL * 32) lanes = 16;      // (the delta rule's lanes exchange a sum per token)
+  const int per = (D + lanes - 1) / lanes;
+  const int DR = per <= 4 ? 4 : (per <= 8 ? 8 : (per <= 16 ? 16 : 32));
+  const int P4 = lanes * (DR > 4 ? DR + 4 : DR);
+  const size_t smem = sizeof(float) * (REC_STAGES * (size_t)REC_TOKENS * ((mode == 0 ? 3 : 2) * P4 + cols + 4) + (size_t)REC_TOKENS * cols * lanes);
+  // 16-byte copies where every row starts on a 16-byte boundary
+  auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  const int vec = (D % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ldv % 4 == 0 && V % 4 == 0 && al(q) && al(k) && al(v) &&
+                   (mode != 0 || (ldd % 4 == 0 && al(dvec)))) ? 1 : 0;
   const dim3 grid((unsigned)n_seqs, (unsigned)H, (unsigned)((V + cols - 1) / cols));
-  const dim3 block((unsigned)cols * 4);
-#define AB_GO(DRV, M)                                                                                                \
-  ab_launch(recurrence_kernel<DRV, M>, grid, block, smem, stream, q, ldq, k, ldk, v, ldv, dvec, ldd, dsc, beta, qscale, \
-            state, out, cu_q, slots, H, Hk, D, V, cols, write_state)
-  if (mode == 0) {
-    if (DR == 8) AB_GO(8, 0); else if (DR == 16) AB_GO(16, 0); else if (DR == 32) AB_GO(32, 0); else AB_GO(64, 0);
-  } else {
-    if (DR == 8) AB_GO(8, 1); else if (DR == 16) AB_GO(16, 1); else if (DR == 32) AB_GO(32, 1); else AB_GO(64, 1);
+  const dim3 block((unsigned)(cols * lanes));
+  bool done = false;
+#define AB_GO(DRV, L, M)                                                                                                  \
+  if (!done && DR == DRV && lanes == L && mode == M) {                                                                    \
+    if (smem > 48 * 1024)                                                                                                 \
+      cudaFuncSetAttribute(recurrence_kernel<DRV, L, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+    ab_launch(recurrence_kernel<DRV, L, M>, grid, block, smem, stream, q, ldq, k, ldk, v, ldv, dvec, ldd, dsc, beta, qscale, \
+              state, out, cu_q, slots, H, Hk, D, V, cols, write_state, vec);                                              \
+    done = true;                                                                                                          \
   }
+#define AB_BOTH(DRV, L) AB_GO(DRV, L, 0) AB_GO(DRV, L, 1)
+  AB_BOTH(4, 8) AB_BOTH(8, 8) AB_BOTH(16, 8) AB_BOTH(32, 8)
+  AB_BOTH(4, 16) AB_BOTH(8, 16) AB_BOTH(16, 16)
+  AB_BOTH(4, 32) AB_BOTH(8, 32)
+#undef AB_BOTH
 #undef AB_GO
+  if (!done) return AB_BAD_ARG;
   return ab_launch_status();
 }
 
-// a[t, c] = sigmoid(z)^(1/tau), z = b[c] + sum_r W2[c, r] y[t, r]; y: `rank` numbers per token at y + t * ldy.
-// A block of 128 channels x 8 tokens, so a row of W2 is read once for eight tokens.
+// a[t, c] = sigmoid(z)^(1/tau), z = b[c] + sum_r W2[c, r] y[t, r]; y: `rank` numbers per token at y + t * ldy; W2 is
+// given transposed, [rank, channels], so that neighbouring threads read neighbouring numbers.
+// A block of 128 channels x 8 tokens, so a column of W2 is read once for eight tokens.
 __global__ void gla_decay_kernel(const float* __restrict__ y, int ldy, const float* __restrict__ w2,
                                  const float* __restrict__ bias, float inv_tau, float* __restrict__ a, int n_tokens,
                                  int channels, int rank) {
@@ -173,9 +319,8 @@ __global__ void gla_decay_kernel(const float* __restrict__ y, int ldy, const flo
   const float bc = bias != nullptr ? bias[c] : 0.f;
 #pragma unroll
   for (int tt = 0; tt < 8; ++tt) z[tt] = bc;
-  const float* wr = w2 + (size_t)c * rank;
   for (int rr = 0; rr < rank; ++rr) {
-    const float w = wr[rr];
+    const float w = w2[(size_t)rr * channels + c];
 #pragma unroll
     for (int tt = 0; tt < 8; ++tt)
       if (tt < n) z[tt] += w * ys[tt * rank + rr];

@@ -1865,14 +1865,16 @@ def gated_recurrence(mode, q, k, v, state, out, ctx, H, Hk, D, V, qscale=1.0, de
     return out
 
 
-def gla_decay(y, w2, bias, tau, out, n_tokens):
-    """out[t, c] = sigmoid(z)^(1/tau) with z = bias[c] + w2[c] . y[t]; y float32 rows of `rank` numbers (a view with a
-    row stride is fine), w2 float32 [channels, rank], out float32 [T, channels]."""
+def gla_decay(y, w2t, bias, tau, out, n_tokens):
+    """out[t, c] = sigmoid(z)^(1/tau) with z = bias[c] + sum_r w2t[r, c] y[t, r]; y float32 rows of `rank` numbers (a
+    view with a row stride is fine), w2t float32 [rank, channels] (the projection's matrix transposed), out float32
+    [T, channels]."""
+    w2 = w2t
     _cuda(y, w2, bias, out)
-    channels, rank = w2.shape
+    rank, channels = w2.shape
     ldy = _f32_rows(y, n_tokens, "y")
     _need(y.shape[1] == rank and y.shape[0] >= n_tokens, "gla_decay: y [T, rank]")
-    _need(w2.dtype == torch.float32 and w2.is_contiguous(), "gla_decay: w2 float32 [channels, rank]")
+    _need(w2.dtype == torch.float32 and w2.is_contiguous(), "gla_decay: w2t float32 [rank, channels]")
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == channels, "gla_decay: bias float32")
     _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[-1] == channels and out.numel() >= n_tokens * channels,

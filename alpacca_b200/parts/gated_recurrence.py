@@ -64,7 +64,8 @@ class GatedLinearAttention(Mixer):
                 ParamSpec(f"{p}.{n[7]}{self.bias_suffix}", (self.H * self.D,), "vector", "normal")]
 
     def load_own(self, fetch):
-        self.norm_weight, self.w_a2, self.b_a2 = (fetch(s) for s in self.own_param_specs())
+        self.norm_weight, w_a2, self.b_a2 = (fetch(s) for s in self.own_param_specs())
+        self.w_a2 = w_a2.t().contiguous()          # [rank, H * D]: what the kernel reads
 
     def cache_spec(self):
         return StateSpec((self.H, self.D, self.V), torch.float32)

@@ -36,6 +36,11 @@ two score maps, attention over its own keys, token inputs, two layers that run t
 `--design sazepel` does the same for the Sazepel decoder (retention; attention with mixed heads beside a retention;
 routed gated experts in every layer), beside the Lefatar decoder (the framework's other decoder with routed experts
 and a matrix state per head) and the Llama decoder.
+`--design mavidra` does the same for the Mavidra decoder (gated linear attention; latent attention with a window, one
+layer reading another's cache; attention with a sink beside the gated delta rule; routed gated experts with sigmoid
+scores in every layer; layer norms around every sub-layer), beside the Sazepel decoder (the closest: recurrent mixers,
+two mixers side by side, routed gated experts of the same sizes, norms around every sub-layer), the Lefatar decoder
+(the same latent-attention kernels) and the Llama decoder.
 
 One JSON line goes to standard output.  With --gpus N > 1 it prints a line that says so and exits
 with 2: this library runs on one GPU.
@@ -542,7 +547,7 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------------------------------------
-# --design lefatar | buguzen | sazepel: that decoder beside the Llama decoder of the same width, depth and dense
+# --design lefatar | buguzen | sazepel | mavidra: that decoder beside the Llama decoder of the same width, depth and dense
 # feed-forward, at sizes that resemble a real model's layers (random weights).
 
 def _lefatar_layers(E, mlstm, latent, dense_ff, moe, n_layers):
@@ -620,6 +625,30 @@ def _sazepel_config(z):
             "logit_scale": 1.0, "layers": [pair[i % 2] for i in range(z["layers"])]}
 
 
+def _mavidra_config(z):
+    """Eight layers in the pattern (gated linear attention, latent attention, attention beside the delta rule, gated
+    linear attention), the second latent-attention layer reading the first one's cache; every layer with routed gated
+    experts of the size of the Sazepel and Lefatar decoders' beside it."""
+    rt = z["moe"]["router"]
+    mlp = {"kind": "moe", "expert": dict(z["moe"]["expert"]),
+           "router": {"experts": rt["experts"], "top": rt["top"], "groups": dict(rt["groups"])}}
+    lin = z["buguzen"]
+    gla = {"type": "gla", "mlp": mlp, "mixer": {"heads": lin["lin_heads"], "dim": lin["lin_dim"], "vdim": lin["lin_vdim"],
+                                                "tau": 16.0, "rank": z["width"] // 16}}
+    lat = {k: v for k, v in z["latent"].items()}
+    lat["mask"] = {"size": lin["window"]}
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head_dim"], "vdim": z["head_dim"],
+            "scale": z["head_dim"] ** -0.5, "rot": {"base": 500000.0, "dims": z["head_dim"] // 2}}
+    right = {"heads": lin["lin_heads"] // 2, "kv_heads": lin["lin_heads"] // 4, "dim": lin["lin_dim"], "vdim": lin["lin_vdim"],
+             "conv": 4}
+    par = {"type": "parallel", "mlp": mlp, "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}}
+    layers = [gla, {"type": "latent_attention", "mixer": lat, "mlp": mlp}, par, gla, gla,
+              {"type": "latent_attention", "mixer": dict(lat, kv_from=1, mask={"size": lin["window"] // 2}), "mlp": mlp}, par, gla]
+    return {"architecture": "Mavidra", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "embedding": {"scale": 8.0, "bigram": {"buckets": 65521, "mul_prev": 257, "mul_cur": 31}},
+            "layers": layers[:z["layers"]]}
+
+
 def design_configs(size, design="lefatar"):
     z = DESIGN_SIZES[size]
     llama = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": z["layers"], "hidden_size": z["width"],
@@ -633,6 +662,8 @@ def design_configs(size, design="lefatar"):
                "layers": _lefatar_layers(z["width"], z["mlstm"], z["latent"], z["dense_ff"], z["moe"], z["layers"])}
     if design == "sazepel":
         return {"sazepel": _sazepel_config(z), "lefatar": lefatar, "llama": llama}
+    if design == "mavidra":
+        return {"mavidra": _mavidra_config(z), "sazepel": _sazepel_config(z), "lefatar": lefatar, "llama": llama}
     return {"lefatar": lefatar, "llama": llama}
 
 
@@ -713,7 +744,7 @@ def main():
                     help="with --only decode: equal prompts of this many tokens instead of the workload's")
     ap.add_argument("--prefill-tokens", type=int, default=0,
                     help="with --only prefill: one prompt of this many tokens instead of the workload's")
-    ap.add_argument("--design", default="", choices=["", "lefatar", "buguzen", "sazepel"],
+    ap.add_argument("--design", default="", choices=["", "lefatar", "buguzen", "sazepel", "mavidra"],
                     help="instead of the benchmark workload: prefill and decode throughput of this design beside the "
                          "Llama decoder of the same width and depth (random weights), one JSON line")
     ap.add_argument("--size", default="", choices=[""] + sorted(DESIGN_SIZES), help="with --design: one size only")

@@ -194,7 +194,7 @@ def test_gated_linear_attention_keeps_and_forgets_by_its_decay(dtype, decode):
     w = short(load_part(part, seed=5, dtype=dtype, std=0.2), "m")
     bias = np.concatenate([np.full(16, 30.0), np.zeros(16)]).astype(np.float32)
     part.b_a2.copy_(torch.from_numpy(bias).cuda())
-    part.w_a2.zero_()
+    part.w_a2.zero_()          # (kept transposed by the part)
     w["a2.b"], w["a2"] = bias.astype(np.float64), np.zeros_like(w["a2"])
     rng = np.random.default_rng(2)
     x64 = rng.normal(0.0, 0.3, (T, width))
