@@ -24,7 +24,8 @@
 #include "launch.cuh"
 
 #define REC_TOKENS 8        // tokens staged per round of the walk
-#define REC_STAGES 4        // rounds whose rows are in flight or in use: the walk of a round is short against the memory's latency
+#define REC_STAGES 4        // rounds whose rows are in flight or in use in a step of many tokens: the walk of a round is short
+                            // against the memory's latency (a step of up to one round per sequence has one buffer)
 #define CONV_MAX_TAPS 16
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
@@ -78,12 +79,11 @@ __device__ __forceinline__ void stage_rows(const RowCopier& w, float* dst, int p
   }
 }
 
-// One token of one thread: its DR rows of column j.  The thread's share of the read-out goes to `share` (shared
-// memory); the shares of a column's lanes are added after the round, so that a decay per channel needs no exchange
+// One token of one thread: its DR rows of column j.  Returns the thread's share of the read-out; the shares of a column's lanes are added after the round, so that a decay per channel needs no exchange
 // between lanes while the tokens are walked.  The delta rule needs one per token: S^T k over all rows.
 template <int DR, int LANES, int MODE>
-__device__ __forceinline__ void walk_token(float (&S)[DR], const float4* __restrict__ qr, const float4* __restrict__ kr,
-                                           const float4* __restrict__ ar, float vj, float g, float bt, float* share) {
+__device__ __forceinline__ float walk_token(float (&S)[DR], const float4* __restrict__ qr, const float4* __restrict__ kr,
+                                            const float4* __restrict__ ar, float vj, float g, float bt) {
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;      // four chains, added in a fixed order
   if (MODE == 0) {
 #pragma unroll
@@ -129,10 +129,10 @@ __device__ __forceinline__ void walk_token(float (&S)[DR], const float4* __restr
       a3 += S[i + 3] * qq.w;
     }
   }
-  *share = (a0 + a1) + (a2 + a3);
+  return (a0 + a1) + (a2 + a3);
 }
 
-template <int DR, int LANES, int MODE>
+template <int DR, int LANES, int MODE, int STAGES>
 __global__ void recurrence_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
                                   const float* __restrict__ v, int ldv, const float* __restrict__ dvec, int ldd,
                                   const float* __restrict__ dsc, const float* __restrict__ beta, float qscale,
@@ -152,14 +152,25 @@ __global__ void recurrence_kernel(const float* __restrict__ q, int ldq, const fl
   // a ring of buffers of a round's tokens: q, k (and the decays) of P4 floats each, CV values, two numbers per token
   constexpr int NV = MODE == 0 ? 3 : 2;
   const int per_buf = REC_TOKENS * (NV * P4 + CV + 4);
-  float* shares = rec_sm + REC_STAGES * per_buf;      // [REC_TOKENS][CV][LANES]: the lanes' shares of a round's read-outs
+  float* shares = rec_sm + STAGES * per_buf;      // [REC_TOKENS][CV][LANES]: the lanes' shares of a round's read-outs
   float S[DR];                                 // rows r * DR .. r * DR + DR - 1 of column j
   float* st = state + ((size_t)slot * H + h) * D * V;
   // The tile of the state comes through shared memory: neighbouring threads fetch neighbouring columns of a row
   // (whole 32-byte pieces of memory), then every thread picks its rows.
-  for (int idx = tid; idx < D * CV; idx += blockDim.x) {
-    const int d = idx / CV, c = idx - d * CV;
-    rec_sm[idx] = col0 + c < V ? st[(size_t)d * V + col0 + c] : 0.f;
+  const int cv_shift = 31 - __clz(CV);         // CV is 8, 16 or 32
+  for (int base = tid; base < D * CV; base += blockDim.x * 8) {      // eight loads in flight per thread
+    float got[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int idx = base + u * blockDim.x;
+      const int d = idx >> cv_shift, c = idx & (CV - 1);
+      got[u] = (idx < D * CV && col0 + c < V) ? st[(size_t)d * V + col0 + c] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int idx = base + u * blockDim.x;
+      if (idx < D * CV) rec_sm[idx] = got[u];
+    }
   }
   __syncthreads();
 #pragma unroll
@@ -169,7 +180,7 @@ __global__ void recurrence_kernel(const float* __restrict__ q, int ldq, const fl
   }
   __syncthreads();
   if (LANES * DR != D)                         // rows behind D are read as zeros
-    for (int idx = tid; idx < REC_STAGES * per_buf; idx += blockDim.x) rec_sm[idx] = 0.f;
+    for (int idx = tid; idx < STAGES * per_buf; idx += blockDim.x) rec_sm[idx] = 0.f;
   const int t0 = cu_q[b], t1 = cu_q[b + 1];
   const int cw = min(CV, V - col0);                        // this tile's columns
   const bool vec_v = vec && (cw & 3) == 0 && (col0 & 3) == 0;
@@ -191,20 +202,20 @@ __global__ void recurrence_kernel(const float* __restrict__ q, int ldq, const fl
     }
     copy_commit();
   };
-  // REC_STAGES - 1 rounds are asked for before the first is walked; every turn of the loop commits one group (an
-  // empty one once the tokens have run out), so that "all but the newest REC_STAGES - 1" is always this round's
+  // STAGES - 1 rounds are asked for before the first is walked; every turn of the loop commits one group (an
+  // empty one once the tokens have run out), so that "all but the newest STAGES - 1" is always this round's
 #pragma unroll
-  for (int i = 0; i < REC_STAGES - 1; ++i) {
+  for (int i = 0; i < STAGES - 1; ++i) {
     if (t0 + i * REC_TOKENS < t1) stage(i, t0 + i * REC_TOKENS);
     else copy_commit();
   }
   int buf = 0;
-  for (int c0 = t0; c0 < t1; c0 += REC_TOKENS, buf = (buf + 1) % REC_STAGES) {
+  for (int c0 = t0; c0 < t1; c0 += REC_TOKENS, buf = (buf + 1) % STAGES) {
     const int n = min(REC_TOKENS, t1 - c0);
-    const int ahead = c0 + (REC_STAGES - 1) * REC_TOKENS;
-    if (ahead < t1) stage((buf + REC_STAGES - 1) % REC_STAGES, ahead);     // into the buffer that the round before left
+    const int ahead = c0 + (STAGES - 1) * REC_TOKENS;
+    if (ahead < t1) stage((buf + STAGES - 1) % STAGES, ahead);     // into the buffer that the round before left
     else copy_commit();
-    copy_wait<REC_STAGES - 1>();
+    copy_wait<STAGES - 1>();
     __syncthreads();
     const float* qs = rec_sm + buf * per_buf + r * DRP;
     const float* ks = qs + REC_TOKENS * P4;
@@ -213,16 +224,23 @@ __global__ void recurrence_kernel(const float* __restrict__ q, int ldq, const fl
     const float* sc = vs + REC_TOKENS * CV;
     float* mine = shares + col * LANES + r;
     if (n == REC_TOKENS) {
+      // a whole round: the shares wait in registers until its last token, so that no store stands between the loads
+      // of one token and the next
+      float sh[REC_TOKENS];
 #pragma unroll
       for (int tt = 0; tt < REC_TOKENS; ++tt)
-        walk_token<DR, LANES, MODE>(S, reinterpret_cast<const float4*>(qs + tt * P4), reinterpret_cast<const float4*>(ks + tt * P4),
-                                    reinterpret_cast<const float4*>(as + tt * P4), vs[tt * CV + col],
-                                    MODE == 1 ? sc[2 * tt] : 0.f, MODE == 1 ? sc[2 * tt + 1] : 0.f, mine + tt * CV * LANES);
+        sh[tt] = walk_token<DR, LANES, MODE>(S, reinterpret_cast<const float4*>(qs + tt * P4),
+                                             reinterpret_cast<const float4*>(ks + tt * P4),
+                                             reinterpret_cast<const float4*>(as + tt * P4), vs[tt * CV + col],
+                                             MODE == 1 ? sc[2 * tt] : 0.f, MODE == 1 ? sc[2 * tt + 1] : 0.f);
+#pragma unroll
+      for (int tt = 0; tt < REC_TOKENS; ++tt) mine[tt * CV * LANES] = sh[tt];
     } else {
       for (int tt = 0; tt < n; ++tt)
-        walk_token<DR, LANES, MODE>(S, reinterpret_cast<const float4*>(qs + tt * P4), reinterpret_cast<const float4*>(ks + tt * P4),
-                                    reinterpret_cast<const float4*>(as + tt * P4), vs[tt * CV + col],
-                                    MODE == 1 ? sc[2 * tt] : 0.f, MODE == 1 ? sc[2 * tt + 1] : 0.f, mine + tt * CV * LANES);
+        mine[tt * CV * LANES] = walk_token<DR, LANES, MODE>(S, reinterpret_cast<const float4*>(qs + tt * P4),
+                                                            reinterpret_cast<const float4*>(ks + tt * P4),
+                                                            reinterpret_cast<const float4*>(as + tt * P4), vs[tt * CV + col],
+                                                            MODE == 1 ? sc[2 * tt] : 0.f, MODE == 1 ? sc[2 * tt + 1] : 0.f);
     }
     __syncthreads();
     // a column's read-out: its lanes' shares, added in lane order
@@ -248,18 +266,18 @@ __global__ void recurrence_kernel(const float* __restrict__ q, int ldq, const fl
   }
   __syncthreads();
   for (int idx = tid; idx < D * CV; idx += blockDim.x) {
-    const int d = idx / CV, c = idx - d * CV;
+    const int d = idx >> cv_shift, c = idx & (CV - 1);
     if (col0 + c < V) st[(size_t)d * V + col0 + c] = rec_sm[idx];
   }
 }
 
 // One walk over the step's tokens.  q, k float32 rows with Hk heads of D (row strides ldq, ldk), v with H heads of V;
 // mode 0: dvec [T, H * D] (row stride ldd); mode 1: dsc, beta [T, H].  state [slots, H, D, V]; out [T, H * V].
-// `cols`: value columns per CTA (8, 16 or 32).
+// `cols`: value columns per CTA (8, 16 or 32).  `one_round`: no sequence brings more than REC_TOKENS tokens.
 AB_API int ab_gated_recurrence(int mode, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
                                const float* dvec, int ldd, const float* dsc, const float* beta, float qscale, float* state,
                                float* out, const int* cu_q, const int* slots, int n_seqs, int H, int Hk, int D, int V,
-                               int cols, int write_state, cudaStream_t stream) {
+                               int cols, int write_state, int one_round, cudaStream_t stream) {
   if (n_seqs <= 0) return AB_OK;
   if (H <= 0 || Hk <= 0 || H % Hk || D <= 0 || D > 256 || V <= 0 || (cols != 8 && cols != 16 && cols != 32)) return AB_BAD_ARG;
   if (!q || !k || !v || !state || !out || !cu_q || !slots) return AB_BAD_ARG;
@@ -272,7 +290,8 @@ AB_API int ab_gated_recurrence(int mode, const float* q, int ldq, const float* k
   const int per = (D + lanes - 1) / lanes;
   const int DR = per <= 4 ? 4 : (per <= 8 ? 8 : (per <= 16 ? 16 : 32));
   const int P4 = lanes * (DR > 4 ? DR + 4 : DR);
-  const size_t smem = sizeof(float) * (REC_STAGES * (size_t)REC_TOKENS * ((mode == 0 ? 3 : 2) * P4 + cols + 4) + (size_t)REC_TOKENS * cols * lanes);
+  const int stages = one_round ? 1 : REC_STAGES;
+  const size_t smem = sizeof(float) * (stages * (size_t)REC_TOKENS * ((mode == 0 ? 3 : 2) * P4 + cols + 4) + (size_t)REC_TOKENS * cols * lanes);
   // 16-byte copies where every row starts on a 16-byte boundary
   auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
   const int vec = (D % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ldv % 4 == 0 && V % 4 == 0 && al(q) && al(k) && al(v) &&
@@ -280,15 +299,15 @@ AB_API int ab_gated_recurrence(int mode, const float* q, int ldq, const float* k
   const dim3 grid((unsigned)n_seqs, (unsigned)H, (unsigned)((V + cols - 1) / cols));
   const dim3 block((unsigned)(cols * lanes));
   bool done = false;
-#define AB_GO(DRV, L, M)                                                                                                  \
-  if (!done && DR == DRV && lanes == L && mode == M) {                                                                    \
+#define AB_GO(DRV, L, M, ST)                                                                                              \
+  if (!done && DR == DRV && lanes == L && mode == M && stages == ST) {                                                    \
     if (smem > 48 * 1024)                                                                                                 \
-      cudaFuncSetAttribute(recurrence_kernel<DRV, L, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
-    ab_launch(recurrence_kernel<DRV, L, M>, grid, block, smem, stream, q, ldq, k, ldk, v, ldv, dvec, ldd, dsc, beta, qscale, \
-              state, out, cu_q, slots, H, Hk, D, V, cols, write_state, vec);                                              \
+      cudaFuncSetAttribute(recurrence_kernel<DRV, L, M, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+    ab_launch(recurrence_kernel<DRV, L, M, ST>, grid, block, smem, stream, q, ldq, k, ldk, v, ldv, dvec, ldd, dsc, beta,  \
+              qscale, state, out, cu_q, slots, H, Hk, D, V, cols, write_state, vec);                                      \
     done = true;                                                                                                          \
   }
-#define AB_BOTH(DRV, L) AB_GO(DRV, L, 0) AB_GO(DRV, L, 1)
+#define AB_BOTH(DRV, L) AB_GO(DRV, L, 0, 1) AB_GO(DRV, L, 1, 1) AB_GO(DRV, L, 0, REC_STAGES) AB_GO(DRV, L, 1, REC_STAGES)
   AB_BOTH(4, 8) AB_BOTH(8, 8) AB_BOTH(16, 8) AB_BOTH(32, 8)
   AB_BOTH(4, 16) AB_BOTH(8, 16) AB_BOTH(16, 16)
   AB_BOTH(4, 32) AB_BOTH(8, 32)

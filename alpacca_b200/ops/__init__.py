@@ -1814,6 +1814,7 @@ def head_gate(y, g, g_stride, n_tokens, H, V):
 
 
 RECURRENCE_MAX_DIM = 256         # key dims per head that the walk holds in registers
+RECURRENCE_ROUND = 8             # tokens of a sequence that the walk stages at a time (REC_TOKENS of the kernel)
 RECURRENCE_CTAS = 296            # CTAs a walk aims at (two per processor): fewer value columns per CTA when few
 #                                  (sequence, head) pairs would leave processors idle
 
@@ -1861,7 +1862,7 @@ def gated_recurrence(mode, q, k, v, state, out, ctx, H, Hk, D, V, qscale=1.0, de
     _check(_lib("gated_recurrence").ab_gated_recurrence(
         0 if mode == "channel" else 1, _p(q), ldq, _p(k), ldk, _p(v), ldv, _p(dvec), ldd, _p(dsc), _p(beta),
         ctypes.c_float(qscale), _p(state), _p(out), _p(ctx.cu_q), _p(ctx.slots), ctx.n_seqs, H, Hk, D, V, cols,
-        1 if write_state else 0, _stream()), "gated_recurrence")
+        1 if write_state else 0, 1 if ctx.max_q_len <= RECURRENCE_ROUND else 0, _stream()), "gated_recurrence")
     return out
 
 
