@@ -319,11 +319,13 @@ AB_API int ab_gated_recurrence(int mode, const float* q, int ldq, const float* k
 
 // a[t, c] = sigmoid(z)^(1/tau), z = b[c] + sum_r W2[c, r] y[t, r]; y: `rank` numbers per token at y + t * ldy; W2 is
 // given transposed, [rank, channels], so that neighbouring threads read neighbouring numbers.
-// A block of 128 channels x 8 tokens, so a column of W2 is read once for eight tokens.
-__global__ void gla_decay_kernel(const float* __restrict__ y, int ldy, const float* __restrict__ w2,
-                                 const float* __restrict__ bias, float inv_tau, float* __restrict__ a, int n_tokens,
-                                 int channels, int rank) {
+// A block of 32 channels x 8 tokens; its four warps each take a quarter of the rank (so that a step of a few tokens
+// still spreads over many blocks and no thread walks the whole rank), and the quarters are added in order.
+__global__ void __launch_bounds__(128)
+gla_decay_kernel(const float* __restrict__ y, int ldy, const float* __restrict__ w2t, const float* __restrict__ bias,
+                 float inv_tau, float* __restrict__ a, int n_tokens, int channels, int rank) {
   extern __shared__ float ys[];              // [8][rank]
+  __shared__ float part[4][8][32];
   pdl_wait();
   pdl_trigger();
   const int t0 = blockIdx.y * 8, n = min(8, n_tokens - t0);
@@ -332,29 +334,40 @@ __global__ void gla_decay_kernel(const float* __restrict__ y, int ldy, const flo
     ys[idx] = y[(size_t)(t0 + tt) * ldy + rr];
   }
   __syncthreads();
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= channels) return;
+  const int lane = threadIdx.x & 31, quarter = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  const int span = (rank + 3) >> 2, r0 = quarter * span, r1 = min(rank, r0 + span);
   float z[8];
+#pragma unroll
+  for (int tt = 0; tt < 8; ++tt) z[tt] = 0.f;
+  if (c < channels)
+    for (int rr = r0; rr < r1; ++rr) {
+      const float w = w2t[(size_t)rr * channels + c];
+#pragma unroll
+      for (int tt = 0; tt < 8; ++tt)
+        if (tt < n) z[tt] += w * ys[tt * rank + rr];
+    }
+#pragma unroll
+  for (int tt = 0; tt < 8; ++tt) part[quarter][tt][lane] = z[tt];
+  __syncthreads();
+  if (c >= channels) return;
   const float bc = bias != nullptr ? bias[c] : 0.f;
 #pragma unroll
-  for (int tt = 0; tt < 8; ++tt) z[tt] = bc;
-  for (int rr = 0; rr < rank; ++rr) {
-    const float w = w2[(size_t)rr * channels + c];
-#pragma unroll
-    for (int tt = 0; tt < 8; ++tt)
-      if (tt < n) z[tt] += w * ys[tt * rank + rr];
+  for (int k = 0; k < 2; ++k) {                // warp w finishes tokens 2w and 2w + 1
+    const int tt = quarter * 2 + k;
+    if (tt < n) {
+      const float zz = bc + ((part[0][tt][lane] + part[1][tt][lane]) + (part[2][tt][lane] + part[3][tt][lane]));
+      a[(size_t)(t0 + tt) * channels + c] = expf(-softplus_f(-zz) * inv_tau);      // log sigmoid(z) = -softplus(-z)
+    }
   }
-#pragma unroll
-  for (int tt = 0; tt < 8; ++tt)
-    if (tt < n) a[(size_t)(t0 + tt) * channels + c] = expf(-softplus_f(-z[tt]) * inv_tau);     // log sigmoid(z) = -softplus(-z)
 }
 
-AB_API int ab_gla_decay(const float* y, int ldy, const float* w2, const float* bias, float tau, float* a, int n_tokens,
+AB_API int ab_gla_decay(const float* y, int ldy, const float* w2t, const float* bias, float tau, float* a, int n_tokens,
                         int channels, int rank, cudaStream_t stream) {
   if (n_tokens <= 0) return AB_OK;
-  if (!y || !w2 || !a || channels <= 0 || rank <= 0 || !(tau > 0.f) || (size_t)rank * 32 > 48 * 1024) return AB_BAD_ARG;
-  const dim3 grid((unsigned)((channels + 127) / 128), (unsigned)((n_tokens + 7) / 8));
-  ab_launch(gla_decay_kernel, grid, dim3(128), (size_t)8 * rank * sizeof(float), stream, y, ldy, w2, bias, 1.0f / tau, a,
+  if (!y || !w2t || !a || channels <= 0 || rank <= 0 || !(tau > 0.f) || (size_t)rank * 32 > 44 * 1024) return AB_BAD_ARG;
+  const dim3 grid((unsigned)((channels + 31) / 32), (unsigned)((n_tokens + 7) / 8));
+  ab_launch(gla_decay_kernel, grid, dim3(128), (size_t)8 * rank * sizeof(float), stream, y, ldy, w2t, bias, 1.0f / tau, a,
             n_tokens, channels, rank);
   return ab_launch_status();
 }

@@ -1880,7 +1880,7 @@ def gla_decay(y, w2t, bias, tau, out, n_tokens):
         _need(bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == channels, "gla_decay: bias float32")
     _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape[-1] == channels and out.numel() >= n_tokens * channels,
           "gla_decay: out float32 [T, channels]")
-    _need(tau > 0 and rank <= 1536, "gla_decay: tau positive, rank up to 1536")
+    _need(tau > 0 and rank <= 1408, "gla_decay: tau positive, rank up to 1408")
     _check(_lib("gated_recurrence").ab_gla_decay(_p(y), ldy, _p(w2), _p(bias), ctypes.c_float(tau), _p(out), n_tokens,
                                                  channels, rank, _stream()), "gla_decay")
     return out
