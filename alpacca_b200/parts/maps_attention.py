@@ -95,10 +95,17 @@ class MapsAttention(Mixer):
         if gate is not None:
             self.gate_offset = sum(r for _, r in sources)
             sources.append((f"{prefix}.{gate}", self.H * self.Dv))
+        pad = 0
         if head_gate is not None:
-            self.gate_offset = sum(r for _, r in sources)
             sources.append((f"{prefix}.{head_gate}", self.H))
-        self.qkv = Linear(opts, width, sources, bias=bias, weight_suffix=weight_suffix, bias_suffix=bias_suffix)
+            # the tcgen05 prefill kernel reads the product's rows as [token, head, dim]: the H gate rows are padded
+            # (with zero rows, at load) so that a token's row stays a whole number of heads
+            if self.Dk == self.Dv and self.Dk in (64, 128) and self.M == 1:
+                pad = self.Dk
+        self.qkv = Linear(opts, width, sources, bias=bias, weight_suffix=weight_suffix, bias_suffix=bias_suffix,
+                          pad_rows_to=pad)
+        if head_gate is not None:
+            self.gate_offset = sum(r for _, r in self.qkv.sources[:-1])
         self.out = Linear(opts, self.H * self.Dv, [(f"{prefix}.{o}", width)], weight_suffix=weight_suffix,
                           out_dtype=out_dtype)
         self.q_weight = self.k_weight = self.sink = self.talk = None

@@ -256,8 +256,11 @@ def left_part(dtype, width, H, G, D, V, scale, base, dims, eps, max_positions=10
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,G,D,V,dims", [(4, 2, 16, 24, 8), (6, 1, 32, 16, 32), (3, 3, 20, 12, 0), (6, 3, 64, 64, 16), (2, 2, 128, 48, 64)])
+@pytest.mark.parametrize("H,G,D,V,dims", [(4, 2, 16, 24, 8), (6, 1, 32, 16, 32), (3, 3, 20, 12, 0), (6, 3, 64, 64, 16), (2, 2, 128, 48, 64),
+                                          (4, 2, 128, 128, 64)])
 def test_gated_attention(dtype, H, G, D, V, dims):
+    """In portions down to one token, and whole (head sizes 64 and 128 with values of the same size then run on the
+    tcgen05 kernel in bfloat16, the sink in its last step)."""
     width, eps = 40, 1e-5
     part, mx = left_part(dtype, width, H, G, D, V, 0.3, 1e4, dims, eps)
     w = short(load_part(part, seed=H + D, dtype=dtype, std=0.3), "m")
@@ -268,6 +271,7 @@ def test_gated_attention(dtype, H, G, D, V, dims):
     hs = PartHarness([part.cache_spec()], dtype)
     s = hs.cache.alloc_slot()
     close(feed(part, hs, s, x, (61, 2, 1, 3, 63, 1, 19)), want, dtype, "attention with a sink and a gate per head")
+    close(feed(part, hs, hs.cache.alloc_slot(), x, (150,)), want, dtype, "the same, whole")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
