@@ -203,7 +203,7 @@ __global__ void recurrence_kernel(const float* __restrict__ q, int ldq, const fl
     copy_commit();
   };
   // STAGES - 1 rounds are asked for before the first is walked; every turn of the loop commits one group (an
-  // empty one once the tokens have run out), so that "all but the newest STAGES - 1" is always this round's
+  // empty one once the tokens have run out), so that "all but the newest STAGES - 1" always covers the rows that the loop is about to walk
 #pragma unroll
   for (int i = 0; i < STAGES - 1; ++i) {
     if (t0 + i * REC_TOKENS < t1) stage(i, t0 + i * REC_TOKENS);
